@@ -160,3 +160,108 @@ def write_config_json(folder: str, config_dict: dict) -> None:
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(config_dict, f, indent=1, sort_keys=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+_TOFILORN_MIXERS = ("mingru", "latent_attention", "hgrn2")
+
+
+def _sub(d: dict, key: str, where: str) -> dict:
+    v = d.get(key)
+    if not isinstance(v, dict):
+        raise ConfigError(f"{where}: '{key}' must be an object")
+    return v
+
+
+@dataclass(frozen=True)
+class TofilornLayer:
+    type: str                   # "mingru" | "latent_attention" | "hgrn2"
+    mixer: dict                 # the mixer's sizes and constants, as config.json gives them
+    ff: Optional[int]           # width of the gated feed-forward, None: the layer has none
+
+
+@dataclass(frozen=True)
+class TofilornConfig:
+    """Tofilorn: a decoder whose layers are listed one by one in config.json, each with one of three token mixers
+    (a gated recurrence, a matrix-state recurrence, windowed attention through a latent) and an optional gated
+    feed-forward, over several float residual streams with learned mixing.  Keys: `vocab`, `width`, `streams`
+    (absent: one plain residual stream), `norm.eps`, `layers[i]` = {type, mixer{...}, mlp: null | {kind: "dense", ff}}.
+    There is no largest position: rotation angles are computed from the position."""
+    vocab: int
+    width: int
+    streams: Optional[int]
+    eps: float
+    layers: tuple
+    torch_dtype: str = "bfloat16"
+
+    architecture = "Tofilorn"
+
+    @classmethod
+    def from_dict(cls, d: dict, where: str = "config.json") -> "TofilornConfig":
+        layers = d.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError(f"{where}: 'layers' must be a non-empty list")
+        streams = d.get("streams")
+        if streams is not None:
+            streams = _need(d, "streams", int, where)
+        out = []
+        for i, layer in enumerate(layers):
+            w = f"{where}: layers[{i}]"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"{w} must be an object")
+            kind = layer.get("type")
+            if kind not in _TOFILORN_MIXERS:
+                raise ConfigError(f"{w}: type {kind!r} is not one of {list(_TOFILORN_MIXERS)}")
+            m = _sub(layer, "mixer", w)
+            if kind == "mingru":
+                _need(m, "width", int, w)
+            elif kind == "hgrn2":
+                for k in ("heads", "dim", "vdim"):
+                    _need(m, k, int, w)
+            else:
+                for k in ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank"):
+                    _need(m, k, int, w)
+                _need(m, "scale", float, w)
+                rot = _sub(m, "rot", w)
+                _need(rot, "dims", int, w + ".rot")
+                _need(rot, "base", float, w + ".rot")
+                if rot["dims"] % 2 or rot["dims"] > m["rot_dim"]:
+                    raise ConfigError(f"{w}: rot.dims {rot['dims']} must be even and at most rot_dim {m['rot_dim']}")
+                sc = rot.get("scaling")
+                if sc is not None:
+                    for k in ("factor", "original", "fast", "slow"):
+                        _need(_sub(rot, "scaling", w), k, float, w + ".rot.scaling")
+                if m.get("mask") is not None:
+                    _need(_sub(m, "mask", w), "size", int, w + ".mask")
+                src = m.get("kv_from")
+                if src is not None:
+                    if isinstance(src, bool) or not isinstance(src, int) or not 0 <= src < i:
+                        raise ConfigError(f"{w}: kv_from {src!r} must name an earlier layer")
+                    other = layers[src]
+                    if not isinstance(other, dict) or other.get("type") != "latent_attention" or \
+                            not isinstance(other.get("mixer"), dict) or other["mixer"].get("kv_from") is not None:
+                        raise ConfigError(f"{w}: kv_from {src} must name a latent_attention layer with keys of its own")
+                    for k in ("kv_rank", "rot_dim"):
+                        if other["mixer"].get(k) != m[k]:
+                            raise ConfigError(f"{w}: {k} differs from that of layer {src}, whose keys it reads")
+            mlp = layer.get("mlp")
+            ff = None
+            if mlp is not None:
+                if not isinstance(mlp, dict) or mlp.get("kind", "dense") != "dense":
+                    raise ConfigError(f"{w}: mlp must be null or of kind 'dense', got {mlp!r}")
+                ff = _need(mlp, "ff", int, w + ".mlp")
+            out.append(TofilornLayer(kind, dict(m), ff))
+        dtype = d.get("torch_dtype", d.get("dtype", "bfloat16"))
+        if not isinstance(dtype, str) or dtype not in _DTYPE_NAMES:
+            raise ConfigError(f"{where}: torch_dtype {dtype!r} is not one of {sorted(set(_DTYPE_NAMES))}")
+        return cls(vocab=_need(d, "vocab", int, where), width=_need(d, "width", int, where), streams=streams,
+                   eps=_need(_sub(d, "norm", where), "eps", float, where + ".norm"), layers=tuple(out),
+                   torch_dtype=_DTYPE_NAMES[dtype])
+
+    def to_dict(self) -> dict:
+        d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.eps},
+             "layers": [{"type": l.type, "mixer": dict(l.mixer), "mlp": None if l.ff is None else {"kind": "dense", "ff": l.ff}}
+                        for l in self.layers]}
+        if self.streams is not None:
+            d["streams"] = self.streams
+        return d

@@ -57,7 +57,7 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
                                const T* kcache, const T* vcache,
                                const int* __restrict__ block_tables, int table_stride,
                                const int* __restrict__ token_req, const int* __restrict__ positions,
-                               const int* __restrict__ skip_single_cu_q, int nh, int kvh, int hd, int block_size,
+                               const int* __restrict__ skip_single_cu_q, int nh, int kvh, int hd, int vd, int block_size,
                                int window, float scale, long num_pages, int* err) {
   extern __shared__ float smem[];
   float* qs = smem;                        // [hd]
@@ -108,7 +108,7 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
 #pragma unroll
       for (int j = 0; j < ATT_MAXD; ++j) {
         const int d = lane + 32 * j;
-        if (d < hd) acc[j] += pk * to_f<T>(vrow[d]);
+        if (d < vd) acc[j] += pk * to_f<T>(vrow[d]);
       }
     }
     m = m_new;
@@ -117,7 +117,7 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
 #pragma unroll
   for (int j = 0; j < ATT_MAXD; ++j) {
     const int d = lane + 32 * j;
-    if (d < hd) accs[warp * hd + d] = acc[j];
+    if (d < vd) accs[warp * hd + d] = acc[j];
   }
   __syncthreads();
   float mm = -INFINITY;
@@ -129,8 +129,8 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
     f[w] = (ms[w] == -INFINITY) ? 0.f : expf(ms[w] - mm);
     lt += ls[w] * f[w];
   }
-  T* orow = out + (size_t)t * nh * hd + (size_t)h * hd;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+  T* orow = out + (size_t)t * nh * vd + (size_t)h * vd;
+  for (int d = threadIdx.x; d < vd; d += blockDim.x) {
     float o = 0.f;
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) o += accs[w * hd + d] * f[w];
@@ -142,26 +142,27 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
 
 using namespace vob;
 
-// q: rows of q_stride elements, head h at h*hd; out [T, nh*hd]; caches [num_pages, kvh, block_size, hd];
-// block_tables [B, table_stride]; token_req [T] (-1: padding); positions [T].
+// q: rows of q_stride elements, head h at h*hd; out [T, nh*vd]; caches [num_pages, kvh, block_size, hd];
+// block_tables [B, table_stride]; token_req [T] (-1: padding); positions [T].  Of a value row the first vd elements are
+// read (vd = hd: all of it; less when keys and values are one row and the key is the longer one).
 VOB_API int vob_paged_attention_generic(const void* q, long q_stride, void* out, const void* kcache, const void* vcache,
                                         const int* block_tables, int table_stride, const int* token_req,
                                         const int* positions, const int* skip_single_cu_q, int T, int nh, int kvh, int hd,
-                                        int block_size,
+                                        int vd, int block_size,
                                         int window, float scale, long num_pages, int dtype, int* err,
                                         cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hd <= 0 || hd % 16 || hd > 512 || kvh <= 0 || nh % kvh || block_size <= 0) return VOB_UNSUPPORTED;
+  if (hd <= 0 || hd % 16 || hd > 512 || kvh <= 0 || nh % kvh || block_size <= 0 || vd <= 0 || vd > hd) return VOB_UNSUPPORTED;
   dim3 grid(T, nh);
   const size_t smem = (size_t)(1 + ATT_WARPS) * hd * sizeof(float);
   if (dtype == VOB_F32)
     return launch_kernel(paged_attention_generic_kernel<float>, grid, ATT_WARPS * 32, smem, stream, (const float*)q, q_stride,
                          (float*)out, (const float*)kcache, (const float*)vcache, block_tables, table_stride, token_req,
-                         positions, skip_single_cu_q, nh, kvh, hd, block_size, window, scale, num_pages, err);
+                         positions, skip_single_cu_q, nh, kvh, hd, vd, block_size, window, scale, num_pages, err);
   if (dtype == VOB_BF16)
     return launch_kernel(paged_attention_generic_kernel<__nv_bfloat16>, grid, ATT_WARPS * 32, smem, stream,
                          (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache,
                          (const __nv_bfloat16*)vcache, block_tables, table_stride, token_req, positions, skip_single_cu_q,
-                         nh, kvh, hd, block_size, window, scale, num_pages, err);
+                         nh, kvh, hd, vd, block_size, window, scale, num_pages, err);
   return VOB_BAD_ARGUMENT;
 }

@@ -1,0 +1,185 @@
+// Attention through a latent: what surrounds the paged attention kernels when keys and values are kept as one
+// low-rank row per token.
+//
+//   latent_prep:   the down-projected row of a token is split into the query latent, the key/value latent and a rotated
+//                  key part shared by all heads; both latents are normalised (vector weights), the shared part is
+//                  rotated by the token's position, and [latent | rotated part | zeros] is written to the token's slot
+//                  of the cache plane.  A layer that borrows another layer's plane only gets its query latent.
+//   head_linear:   y[t, h, :] = W_h x[t, h, :] for per-head matrices W_h: queries carried into the latent's space (so
+//                  that a score is a dot product with the cached row itself) and attention results carried from the
+//                  latent's space to the value heads.
+//   latent_query_rotate: the rotated part of every query head, behind its latent part, and zeros up to the row width.
+//
+// The angle of pair i at position p is float(p) * frequency[i], computed where it is used (no table, no position limit);
+// cos and sin are multiplied by an amplitude.  Norms, angles and rotation are float; rows are of the model's type T.
+#include "common.cuh"
+
+namespace vob {
+
+// (a, b) turned by `angle`, amplitude `amp`; products and sums are spelled out so that every kernel rounds alike.
+__device__ __forceinline__ void turn_pair(float a, float b, float angle, float amp, float& ra, float& rb) {
+  const float c = __fmul_rn(cosf(angle), amp), s = __fmul_rn(sinf(angle), amp);
+  ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+  rb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
+}
+
+constexpr int LP_NT = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(LP_NT)
+latent_prep_kernel(const T* down, long stride, const float* __restrict__ wq, const float* __restrict__ wkv,
+                   const float* __restrict__ freq, float amp, const int* __restrict__ positions, const int* __restrict__ slots,
+                   T* cq, T* cache, int q_rank, int kv_rank, int rot, int rotary, int row_width, long num_slots, float eps,
+                   int has_kv, int* err) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int slot = has_kv ? slots[t] : -1;
+  pdl_wait();
+  const T* row = down + (size_t)t * stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < q_rank; i += LP_NT) {
+    const float v = to_f<T>(row[i]);
+    ss += v * v;
+  }
+  float denom = sqrtf(block_sum<LP_NT>(ss, scratch) / (float)q_rank + eps);
+  for (int i = threadIdx.x; i < q_rank; i += LP_NT) cq[(size_t)t * q_rank + i] = from_f<T>(to_f<T>(row[i]) / denom * wq[i]);
+  if (!has_kv || slot < 0) return;       // a borrowed plane, or a padded row of a fixed-size launch
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(err, VOB_ERR_SLOT);
+    return;
+  }
+  const T* kv = row + q_rank;
+  T* dst = cache + (size_t)slot * row_width;
+  ss = 0.f;
+  for (int i = threadIdx.x; i < kv_rank; i += LP_NT) {
+    const float v = to_f<T>(kv[i]);
+    ss += v * v;
+  }
+  denom = sqrtf(block_sum<LP_NT>(ss, scratch) / (float)kv_rank + eps);
+  for (int i = threadIdx.x; i < kv_rank; i += LP_NT) dst[i] = from_f<T>(to_f<T>(kv[i]) / denom * wkv[i]);
+  const T* kr = kv + kv_rank;
+  for (int p = threadIdx.x; p < rot / 2; p += LP_NT) {
+    float a = to_f<T>(kr[2 * p]), b = to_f<T>(kr[2 * p + 1]);
+    if (2 * p + 1 < rotary) turn_pair(a, b, __fmul_rn((float)pos, freq[p]), amp, a, b);
+    dst[kv_rank + 2 * p] = from_f<T>(a);
+    dst[kv_rank + 2 * p + 1] = from_f<T>(b);
+  }
+  if ((rot & 1) && threadIdx.x == 0) dst[kv_rank + rot - 1] = kr[rot - 1];
+  for (int i = kv_rank + rot + threadIdx.x; i < row_width; i += LP_NT) dst[i] = from_f<T>(0.f);
+}
+
+// q [tokens, heads, dk + rot] -> qa[t, h, offset + i] = rotated part (i < rot), 0 (offset + i < row_width).
+template <typename T>
+__global__ void latent_query_rotate_kernel(const T* q, T* qa, const float* __restrict__ freq, float amp,
+                                           const int* __restrict__ positions, int heads, int dk, int rot, int rotary, int offset,
+                                           int row_width) {
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  pdl_wait();
+  const int tail = row_width - offset;
+  for (int idx = threadIdx.x; idx < heads * tail; idx += blockDim.x) {
+    const int h = idx / tail, i = idx % tail;
+    float v = 0.f;
+    if (i < rot) {
+      const T* src = q + ((size_t)t * heads + h) * (dk + rot) + dk;
+      v = to_f<T>(src[i]);
+      if ((i | 1) < rotary) {
+        float a = to_f<T>(src[i & ~1]), b = to_f<T>(src[i | 1]), ra, rb;
+        turn_pair(a, b, __fmul_rn((float)pos, freq[i >> 1]), amp, ra, rb);
+        v = (i & 1) ? rb : ra;
+      }
+    }
+    qa[((size_t)t * heads + h) * row_width + offset + i] = from_f<T>(v);
+  }
+}
+
+// y[t, h, o] = sum_i w[h][i][o] * x[t, h, i]; w is [heads, I, O] with O contiguous.  A block takes HL_TT tokens, one head and 128
+// outputs: the tokens' inputs wait in shared memory as floats and every weight is read once for all of them.  Each output is one
+// chain of multiply-adds over i in ascending order, whatever the tile it falls into.
+constexpr int HL_TT = 8, HL_NT = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(HL_NT)
+head_linear_kernel(const T* x, long x_ts, long x_hs, const T* __restrict__ w, T* y, long y_ts, long y_hs, int tokens, int I, int O) {
+  extern __shared__ float xs[];  // [HL_TT][I]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.y, t0 = blockIdx.z * HL_TT, o = blockIdx.x * HL_NT + threadIdx.x;
+  const int n = min(HL_TT, tokens - t0);
+  for (int idx = threadIdx.x; idx < HL_TT * I; idx += HL_NT) {
+    const int tt = idx / I, i = idx % I;
+    xs[idx] = tt < n ? to_f<T>(x[(size_t)(t0 + tt) * x_ts + (size_t)h * x_hs + i]) : 0.f;
+  }
+  __syncthreads();
+  if (o >= O) return;
+  float acc[HL_TT];
+#pragma unroll
+  for (int tt = 0; tt < HL_TT; ++tt) acc[tt] = 0.f;
+  const T* wh = w + (size_t)h * I * O + o;
+  for (int i = 0; i < I; ++i) {
+    const float wv = to_f<T>(wh[(size_t)i * O]);
+#pragma unroll
+    for (int tt = 0; tt < HL_TT; ++tt) acc[tt] = fmaf(wv, xs[tt * I + i], acc[tt]);
+  }
+#pragma unroll
+  for (int tt = 0; tt < HL_TT; ++tt)
+    if (tt < n) y[(size_t)(t0 + tt) * y_ts + (size_t)h * y_hs + o] = from_f<T>(acc[tt]);
+}
+
+}  // namespace vob
+
+using namespace vob;
+
+// down [T, >= q_rank (+ kv_rank + rot)] rows of `stride` elements; wq [q_rank], wkv [kv_rank], freq [rotary/2] float;
+// cq [T, q_rank]; cache: rows of row_width elements, one per slot; slots [T] (-1: skip).
+VOB_API int vob_latent_prep(const void* down, long stride, const float* wq, const float* wkv, const float* freq, float amp,
+                            const int* positions, const int* slots, void* cq, void* cache, int T, int q_rank, int kv_rank, int rot,
+                            int rotary, int row_width, long num_slots, float eps, int has_kv, int dtype, int* err,
+                            cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (q_rank <= 0 || (has_kv && (kv_rank <= 0 || rot < 0 || rotary > rot || (rotary & 1) || row_width < kv_rank + rot)))
+    return VOB_BAD_ARGUMENT;
+  if (dtype == VOB_F32)
+    return launch_kernel(latent_prep_kernel<float>, dim3(T), dim3(LP_NT), 0, stream, (const float*)down, stride, wq, wkv, freq, amp,
+                         positions, slots, (float*)cq, (float*)cache, q_rank, kv_rank, rot, rotary, row_width, num_slots, eps, has_kv,
+                         err);
+  if (dtype == VOB_BF16)
+    return launch_kernel(latent_prep_kernel<__nv_bfloat16>, dim3(T), dim3(LP_NT), 0, stream, (const __nv_bfloat16*)down, stride, wq,
+                         wkv, freq, amp, positions, slots, (__nv_bfloat16*)cq, (__nv_bfloat16*)cache, q_rank, kv_rank, rot, rotary,
+                         row_width, num_slots, eps, has_kv, err);
+  return VOB_BAD_ARGUMENT;
+}
+
+VOB_API int vob_latent_query_rotate(const void* q, void* qa, const float* freq, float amp, const int* positions, int T, int heads,
+                                    int dk, int rot, int rotary, int offset, int row_width, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (rotary > rot || (rotary & 1) || offset + rot > row_width) return VOB_BAD_ARGUMENT;
+  if (row_width == offset) return 0;
+  if (dtype == VOB_F32)
+    return launch_kernel(latent_query_rotate_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)q, (float*)qa, freq, amp,
+                         positions, heads, dk, rot, rotary, offset, row_width);
+  if (dtype == VOB_BF16)
+    return launch_kernel(latent_query_rotate_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)q,
+                         (__nv_bfloat16*)qa, freq, amp, positions, heads, dk, rot, rotary, offset, row_width);
+  return VOB_BAD_ARGUMENT;
+}
+
+// x: token stride x_ts, head stride x_hs (elements); w [heads, I, O]; y likewise.
+VOB_API int vob_head_linear(const void* x, long x_ts, long x_hs, const void* w, void* y, long y_ts, long y_hs, int T, int heads,
+                            int I, int O, int dtype, cudaStream_t stream) {
+  if (T <= 0 || heads <= 0 || O <= 0) return 0;
+  if (I <= 0) return VOB_BAD_ARGUMENT;
+  const size_t smem = (size_t)HL_TT * I * sizeof(float);
+  dim3 grid((O + HL_NT - 1) / HL_NT, heads, (T + HL_TT - 1) / HL_TT);
+  if (smem > 48 * 1024 || grid.y > 65535 || grid.z > 65535) return VOB_UNSUPPORTED;
+  if (dtype == VOB_F32)
+    return launch_kernel(head_linear_kernel<float>, grid, dim3(HL_NT), smem, stream, (const float*)x, x_ts, x_hs, (const float*)w,
+                         (float*)y, y_ts, y_hs, T, I, O);
+  if (dtype == VOB_BF16)
+    return launch_kernel(head_linear_kernel<__nv_bfloat16>, grid, dim3(HL_NT), smem, stream, (const __nv_bfloat16*)x, x_ts, x_hs,
+                         (const __nv_bfloat16*)w, (__nv_bfloat16*)y, y_ts, y_hs, T, I, O);
+  return VOB_BAD_ARGUMENT;
+}

@@ -172,12 +172,19 @@ class EngineCore:
                              torch.empty(layout.total, dtype=torch.int32, device=self.device))
             counts = self._fill_fixed(g, fill)
             ctx = self._graph_context(g, counts)
+            # the run outside capture really steps the model: pages are rewritten with the same values by the replay, but
+            # per-request state would advance twice, so it is put back before the graph runs
+            kept = [None if s is None else s.clone() for s in self.cache.states] if self.cache.has_states else []
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):          # once outside capture: buffers, library handles, attributes
                 hidden, residual = self.model.forward(ctx)
                 self.model.compute_logits(hidden, residual, ctx)
             torch.cuda.current_stream().wait_stream(side)
+            for s, k in zip(self.cache.states, kept):
+                if s is not None:
+                    s.copy_(k)
+            del kept
             torch.cuda.synchronize()
             g.graph = torch.cuda.CUDAGraph()
             before = kernels.launch_count

@@ -108,11 +108,14 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True, help="tokens the cache pool is made for")
     ap.add_argument("--block-size", type=int, default=64, help="tokens per cache page (default 64)")
+    ap.add_argument("--max-live", type=int, default=4,
+                    help="requests that may be live at once: the state slots the engine is made with (default 4)")
     ap.add_argument("--prefix-caching", action="store_true",
                     help="a request's first entry starts on the full pages that an earlier request computed for the same tokens")
     args = ap.parse_args(argv)
     os.makedirs(args.out, exist_ok=True)
-    runner = TraceRunner(args.model, args.dtype, args.max_tokens, args.block_size, prefix_caching=args.prefix_caching)
+    runner = TraceRunner(args.model, args.dtype, args.max_tokens, args.block_size, max_live=args.max_live,
+                         prefix_caching=args.prefix_caching)
     for line in sys.stdin:
         line = line.strip()
         if not line:

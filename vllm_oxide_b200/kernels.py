@@ -186,6 +186,8 @@ def qk_norm_rope_kv_write(qkv, bias, positions, slots, wq, wk, rule, kcache, vca
     `RotationRule` (table [max_pos, rotary_dim] float32, rotary_dim, interleaved); a rule with rotary_dim 0 rotates
     nothing."""
     table = rule.table if rule.rotary_dim > 0 else None
+    if rule.rotary_dim > 0 and table is None:
+        raise KernelError("this kernel rotates by a table of angles; the rule has none (a part made with table=False)")
     _cuda(qkv, positions, slots, table, kcache, vcache)
     if table is not None and (table.dtype != torch.float32 or table.shape[1] != rule.rotary_dim or not table.is_contiguous()):
         raise KernelError(f"the table of angles must be contiguous float32 [max_pos, {rule.rotary_dim}]")
@@ -200,15 +202,115 @@ def qk_norm_rope_kv_write(qkv, bias, positions, slots, wq, wk, rule, kcache, vca
 
 
 def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, token_req, positions, num_tokens, nh, kvh,
-                            hd, window: int, scale: float, err, skip_single_cu_q=None) -> None:
+                            hd, window: int, scale: float, err, skip_single_cu_q=None, value_dim: Optional[int] = None) -> None:
     """Every token of the batch; with `skip_single_cu_q` (the batch's cu_q) the tokens of requests that
-    bring exactly one token are left to the decode kernel."""
+    bring exactly one token are left to the decode kernel.  `value_dim`: only that many leading elements of a value
+    row are read and `out` is [tokens, nh * value_dim] (keys and values may then be one and the same plane)."""
     _cuda(q, out, kcache, vcache, block_tables, token_req, positions)
     _check(lib().vob_paged_attention_generic(_p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache),
                                              _p(block_tables), block_tables.shape[-1], _p(token_req), _p(positions),
-                                             _p(skip_single_cu_q), num_tokens, nh, kvh, hd, kcache.shape[2], window,
+                                             _p(skip_single_cu_q), num_tokens, nh, kvh, hd,
+                                             hd if value_dim is None else int(value_dim), kcache.shape[2], window,
                                              ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), _code(q.dtype),
                                              _p(err), _stream()), "paged_attention_generic")
+
+
+def stream_step(streams, num_streams: int, width: int, eps: float, err, y=None, init=None, mix=None, out_w=None, in_w=None,
+                gain=None, normed=None, rows=None, n_out: Optional[int] = None) -> None:
+    """One pass over the residual streams (float [tokens, num_streams * width]).  `init` [tokens, width]: every stream
+    becomes the embedded token; else with `y` [tokens, width]: new stream t = sum_s mix[s, t] * stream s + out_w[t] * y.
+    With `normed` [rows, width]: u = sum_s in_w[s] * stream s, normed = u / sqrt(mean(u^2) + eps) * gain.  Missing
+    coefficients are the identity, ones and 1.  With `rows` (source rows, `n_out` of them) only the combination is
+    computed, for those rows, and no stream is written."""
+    _cuda(streams, y, init, mix, out_w, in_w, gain, normed, rows)
+    assert streams.dtype == torch.float32 and streams.is_contiguous() and streams.shape[1] == num_streams * width
+    n_src = streams.shape[0]
+    n = n_src if rows is None else int(n_out)
+    act = next((t for t in (normed, y, init) if t is not None), None)
+    for t in (mix, out_w, in_w, gain):
+        assert t is None or t.dtype == torch.float32
+    for t in (y, init, normed):
+        assert t is None or (t.dtype == act.dtype and t.is_contiguous() and t.shape[1] == width)
+    _check(lib().vob_stream_step(_p(streams), _p(y), _p(init), _p(mix), _p(out_w), _p(in_w), _p(gain), _p(normed), _p(rows),
+                                 n, n_src, num_streams, width, ctypes.c_float(eps),
+                                 _code(act.dtype if act is not None else torch.float32), _p(err), _stream()), "stream_step")
+
+
+def stream_sum(streams, sums, num_streams: int, width: int) -> None:
+    """sums [tokens, width] (float) = the sum of a token's streams."""
+    _cuda(streams, sums)
+    assert streams.dtype == sums.dtype == torch.float32 and streams.is_contiguous() and sums.is_contiguous()
+    _check(lib().vob_stream_sum(_p(streams), _p(sums), sums.shape[0], num_streams, width, _stream()), "stream_sum")
+
+
+def mingru_scan(zxg, bias_z, bias_x, state, cu_q, state_slots, out, num_requests: int, err) -> None:
+    """The gated recurrence s = (1 - z) s + z * candidate over every request's tokens of this step, from and to its
+    state slot (float [slots, width]); zxg [tokens, 3 * width] holds the pre-activations z | candidate | output gate."""
+    _cuda(zxg, bias_z, bias_x, state, cu_q, state_slots, out)
+    W = out.shape[1]
+    assert zxg.is_contiguous() and out.is_contiguous() and zxg.shape[1] == 3 * W and state.dtype == torch.float32
+    assert state.is_contiguous() and state.shape[1] == W and bias_z.dtype == zxg.dtype == bias_x.dtype == out.dtype
+    _check(lib().vob_mingru_scan(_p(zxg), _p(bias_z), _p(bias_x), _p(state), _p(cu_q), _p(state_slots), _p(out),
+                                 num_requests, W, state.shape[0], _code(out.dtype), _p(err), _stream()), "mingru_scan")
+
+
+def hgrn2_scan(qfv, bias_f, lower, norm_weight, state, cu_q, state_slots, out, num_requests: int, heads: int, dk: int,
+               dv: int, eps: float, err, raw=None) -> None:
+    """The matrix-state recurrence M = diag(f) M + (1 - f) v^T, o = M^T q, with the per-head norm of o, over every
+    request's tokens of this step; state float [slots, heads, dk, dv]; qfv [tokens, heads * (2 dk + dv)].  `raw`
+    (float [tokens, heads * dv]) is needed when dv > 128."""
+    _cuda(qfv, bias_f, lower, norm_weight, state, cu_q, state_slots, out, raw)
+    T = out.shape[0]
+    assert qfv.is_contiguous() and out.is_contiguous() and qfv.shape[1] == heads * (2 * dk + dv) and out.shape[1] == heads * dv
+    assert state.dtype == torch.float32 and state.is_contiguous() and state[0].numel() == heads * dk * dv
+    assert lower.dtype == torch.float32 and norm_weight.dtype == torch.float32 and bias_f.dtype == qfv.dtype == out.dtype
+    _check(lib().vob_hgrn2_scan(_p(qfv), _p(bias_f), _p(lower), _p(norm_weight), _p(state), _p(cu_q), _p(state_slots),
+                                _p(out), _p(raw), T, num_requests, heads, dk, dv, ctypes.c_float(eps), state.shape[0],
+                                _code(out.dtype), _p(err), _stream()), "hgrn2_scan")
+
+
+def latent_prep(down, wq, wkv, rule, positions, slots, cq, cache, num_tokens: int, q_rank: int, kv_rank: int, rot: int,
+                eps: float, write_kv: bool, err) -> None:
+    """A token's down-projected row [query latent | key/value latent | shared key part] -> the normalised query latent in
+    `cq`, and, with `write_kv`, [normalised latent | shared part rotated by `rule` | zeros] in the token's row of `cache`
+    ([pages, 1, page size, row width])."""
+    _cuda(down, wq, wkv, rule.frequencies, positions, slots, cq, cache)
+    assert down.stride(1) == 1 and cq.is_contiguous() and wq.dtype == torch.float32
+    row_width = num_slots = 0
+    if write_kv:
+        assert cache.is_contiguous() and cache.shape[1] == 1 and wkv.dtype == torch.float32 and cache.dtype == down.dtype
+        row_width, num_slots = cache.shape[3], cache.shape[0] * cache.shape[2]
+        if rule.rotary_dim > 0 and (rule.frequencies is None or not rule.interleaved):
+            raise KernelError("latent_prep rotates neighbouring pairs by computed angles: the rule needs `frequencies` "
+                              "and `interleaved`")
+    _check(lib().vob_latent_prep(_p(down), ctypes.c_long(down.stride(0)), _p(wq), _p(wkv), _p(rule.frequencies),
+                                 ctypes.c_float(rule.amplitude), _p(positions), _p(slots), _p(cq), _p(cache), num_tokens,
+                                 q_rank, kv_rank, rot, rule.rotary_dim, row_width, ctypes.c_long(num_slots),
+                                 ctypes.c_float(eps), int(write_kv), _code(down.dtype), _p(err), _stream()), "latent_prep")
+
+
+def latent_query_rotate(q, qa, rule, positions, num_tokens: int, heads: int, dk: int, rot: int, offset: int,
+                        row_width: int) -> None:
+    """qa[t, h, offset:offset+rot] = the last `rot` elements of query head h of q [tokens, heads * (dk + rot)], rotated by
+    `rule`; zeros behind, up to row_width."""
+    _cuda(q, qa, rule.frequencies, positions)
+    assert q.is_contiguous() and qa.is_contiguous() and q.dtype == qa.dtype
+    if rule.rotary_dim > 0 and (rule.frequencies is None or not rule.interleaved):
+        raise KernelError("latent_query_rotate needs a rule with `frequencies` and `interleaved`")
+    _check(lib().vob_latent_query_rotate(_p(q), _p(qa), _p(rule.frequencies), ctypes.c_float(rule.amplitude), _p(positions),
+                                         num_tokens, heads, dk, rot, rule.rotary_dim, offset, row_width, _code(q.dtype),
+                                         _stream()), "latent_query_rotate")
+
+
+def head_linear(x, x_token_stride: int, x_head_stride: int, w, y, y_token_stride: int, y_head_stride: int, num_tokens: int) -> None:
+    """y[t, h, :O] = sum_i w[h, i, :] * x[t, h, i] for per-head matrices w [heads, I, O]; x and y are addressed by token
+    and head strides (elements), so either may be a slice of wider rows."""
+    _cuda(x, w, y)
+    assert w.is_contiguous() and w.dim() == 3 and x.dtype == w.dtype == y.dtype
+    heads, I, O = w.shape
+    _check(lib().vob_head_linear(_p(x), ctypes.c_long(x_token_stride), ctypes.c_long(x_head_stride), _p(w), _p(y),
+                                 ctypes.c_long(y_token_stride), ctypes.c_long(y_head_stride), num_tokens, heads, I, O,
+                                 _code(x.dtype), _stream()), "head_linear")
 
 
 def attention_decode_scratch_floats(head_dim: int, num_requests: int, nh: int, num_splits: int) -> int:

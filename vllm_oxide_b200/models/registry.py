@@ -1,4 +1,4 @@
-"""One registry from the architecture's name (config.json `architectures[0]`) to its model.
+"""One registry from the architecture's name (config.json `architectures[0]`, or `architecture`) to its model.
 
 As in the reference (vllm-oxide, crates/vllm-oxide/src/models/registry.rs:10-51) an unknown name
 is an error that lists the supported ones.  An entry is (typed configuration class, plan function).
@@ -7,9 +7,10 @@ from __future__ import annotations
 
 from typing import Callable, Dict, Tuple
 
-from ..config.model_config import ConfigError, Qwen3Config
+from ..config.model_config import ConfigError, Qwen3Config, TofilornConfig
 from .plan import ModelPlan
 from .qwen3 import qwen3_plan
+from .tofilorn import tofilorn_plan
 
 _ARCHITECTURES: Dict[str, Tuple[Callable[[dict], object], Callable[[object], ModelPlan]]] = {}
 
@@ -26,8 +27,10 @@ def supported_architectures():
 def resolve(config_dict: dict, where: str = "config.json"):
     """(typed config, plan) for a parsed config.json."""
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]      # some configurations name their one architecture directly
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError(f"{where}: 'architectures' must be a non-empty list of names")
+        raise ConfigError(f"{where}: 'architectures' must be a non-empty list of names (or 'architecture' a name)")
     name = archs[0]
     if name not in _ARCHITECTURES:
         raise ConfigError(f"{where}: architecture {name!r} is not supported; supported: {supported_architectures()}")
@@ -37,3 +40,4 @@ def resolve(config_dict: dict, where: str = "config.json"):
 
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict, qwen3_plan)
+register_architecture("Tofilorn", TofilornConfig.from_dict, tofilorn_plan)

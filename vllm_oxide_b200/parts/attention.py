@@ -134,25 +134,35 @@ class Attention(Mixer):
         return left
 
     def attend(self, qkv, q_stride, out, cache, ctx, T):
-        """bfloat16: decoding requests (one token) go to the split-key tensor-core kernel, requests with a
-        portion to the tensor-core kernel for portions.  The 32-bit path, and sizes those kernels refuse,
-        go to the plain kernel."""
-        tables = ctx.block_tables[cache.group]
-        if not kernels.has_fast_attention(qkv.dtype, self.hd, self.nh // self.kvh):
-            kernels.paged_attention_generic(qkv, q_stride, out, cache.k, cache.v, tables, ctx.token_req, ctx.positions, T,
-                                            self.nh, self.kvh, self.hd, self.window, self.scale, ctx.err)
-            return
-        B = ctx.launch_requests
-        if ctx.num_decode > 0:
-            keys = ctx.max_context if self.window == 0 else min(ctx.max_context, self.window)
-            splits = decode_splits(B, self.kvh, keys, kernels.sm_count())
-            n = kernels.attention_decode_scratch_floats(self.hd, B, self.nh, splits)
-            scratch = ctx.ws.get_flat("attention_decode_scratch", n, torch.float32) if n else None
-            kernels.attention_decode(qkv, q_stride, out, cache.k, cache.v, tables, ctx.cu_q, ctx.context_lens, B, self.nh,
-                                     self.kvh, self.hd, self.window, self.scale, splits, scratch, ctx.err, pairs=self._pairs)
-        if ctx.max_q > 1:
-            kernels.attention_prefill(qkv, q_stride, out, cache.k, cache.v, tables, ctx.cu_q, ctx.context_lens, B,
-                                      ctx.max_q, self.nh, self.kvh, self.hd, self.window, self.scale, ctx.err)
+        paged_attend(qkv, q_stride, out, cache.k, cache.v, cache.group, ctx, T, self.nh, self.kvh, self.hd, self.window,
+                     self.scale, self._pairs)
+
+
+def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: int, kvh: int, hd: int, window: int,
+                 scale: float, pairs=None, value_dim=None) -> int:
+    """Attention of every query of the step over the pages of `keys` / `values`; returns the width of a head in `out`.
+    bfloat16: decoding requests (one token) go to the split-key tensor-core kernel, requests with a portion to the
+    tensor-core kernel for portions.  The 32-bit path, and sizes those kernels refuse, go to the plain kernel.
+    `value_dim` (keys and values are one plane whose rows begin with the value): the plain kernel reads and writes only
+    that much of a value row; the tensor-core kernels take whole rows, and the caller uses the first `value_dim`
+    elements of each head of `out`."""
+    tables = ctx.block_tables[group]
+    if not kernels.has_fast_attention(q.dtype, hd, nh // kvh):
+        kernels.paged_attention_generic(q, q_stride, out, keys, values, tables, ctx.token_req, ctx.positions, T,
+                                        nh, kvh, hd, window, scale, ctx.err, value_dim=value_dim)
+        return hd if value_dim is None else value_dim
+    B = ctx.launch_requests
+    if ctx.num_decode > 0:
+        n_keys = ctx.max_context if window == 0 else min(ctx.max_context, window)
+        splits = decode_splits(B, kvh, n_keys, kernels.sm_count())
+        n = kernels.attention_decode_scratch_floats(hd, B, nh, splits)
+        scratch = ctx.ws.get_flat("attention_decode_scratch", n, torch.float32) if n else None
+        kernels.attention_decode(q, q_stride, out, keys, values, tables, ctx.cu_q, ctx.context_lens, B, nh,
+                                 kvh, hd, window, scale, splits, scratch, ctx.err, pairs=pairs)
+    if ctx.max_q > 1:
+        kernels.attention_prefill(q, q_stride, out, keys, values, tables, ctx.cu_q, ctx.context_lens, B,
+                                  ctx.max_q, nh, kvh, hd, window, scale, ctx.err)
+    return hd
 
 
 DECODE_BLOCKS_PER_SM = 2   # blocks of the decode attention kernel that fit an SM (its shared memory decides)

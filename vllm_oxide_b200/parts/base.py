@@ -160,10 +160,15 @@ class Norm(Part):
 class RotationRule:
     """What a mixer's kernel needs of a rotary position encoding: the first `rotary_dim` elements of every query and key
     head are rotated (0: none), in pairs (i, i + rotary_dim/2) or, `interleaved`, in pairs (2i, 2i + 1), by the angles of
-    the token's position in `table`: float32 [max_position, rotary_dim], cos of rotary_dim/2 angles, then their sin."""
+    the token's position in `table`: float32 [max_position, rotary_dim], cos of rotary_dim/2 angles, then their sin.
+    A rule may instead (or also) give `frequencies` (float32 [rotary_dim/2]) and `amplitude`: the angle of pair i at
+    position p is then float(p) * frequencies[i], computed by the kernel where it is used, cos and sin both times
+    `amplitude`; such a rule has no largest position."""
     table: Optional[torch.Tensor]
     rotary_dim: int
     interleaved: bool = False
+    frequencies: Optional[torch.Tensor] = None
+    amplitude: float = 1.0
 
 
 NO_ROTATION = RotationRule(None, 0, False)

@@ -15,20 +15,21 @@ from .linear import linear, linear_into_stream, tc5_product
 class SwiGLU(FeedForward):
     graph_safe = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, **_):
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str,
+                 names=("gate_proj.weight", "up_proj.weight", "down_proj.weight"), **_):
+        """`names`: what the checkpoint calls the gate, up and down matrices behind `prefix`."""
         self.H, self.I, self.prefix = hidden_size, intermediate_size, prefix
+        self.n_gate, self.n_up, self.n_down = (prefix + n for n in names)
         self.wgu = self.wdown = None
         self.interleaved = False
 
     def tensor_specs(self) -> List[TensorSpec]:
-        p = self.prefix
-        return [TensorSpec(p + "gate_proj.weight", (self.I, self.H), "matrix", self.H),
-                TensorSpec(p + "up_proj.weight", (self.I, self.H), "matrix", self.H),
-                TensorSpec(p + "down_proj.weight", (self.H, self.I), "matrix", self.I)]
+        return [TensorSpec(self.n_gate, (self.I, self.H), "matrix", self.H),
+                TensorSpec(self.n_up, (self.I, self.H), "matrix", self.H),
+                TensorSpec(self.n_down, (self.H, self.I), "matrix", self.I)]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        p = self.prefix
-        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        gate, up = tensors[self.n_gate], tensors[self.n_up]
         self.interleaved = self.I % 8 == 0
         if self.interleaved:
             # groups of eight gate rows followed by the eight up rows of the same outputs: one 16-row tile of the
@@ -38,7 +39,7 @@ class SwiGLU(FeedForward):
         else:
             # rows of gate, then up (crates/vllm-oxide/src/layers/linear.rs:132-138)
             self.wgu = torch.cat([gate, up], dim=0).contiguous()
-        self.wdown = tensors[p + "down_proj.weight"].contiguous()
+        self.wdown = tensors[self.n_down].contiguous()
 
     adds_into_stream = True
 

@@ -15,7 +15,8 @@ kept in the list the caller passes as `unexpected`, and never read; `strict=True
 error too.
 
 Kept dtypes: matrices and embeddings in the model dtype (bfloat16 when serving, float32
-on the true 32-bit path); norm weights always in float32, so a norm weight stored in
+on the true 32-bit path); norm weights and coefficients (small learned numbers that enter
+float arithmetic: stream mixing weights, lower bounds of gates) always in float32, so one stored in
 32-bit stays so; integer tensors as int32.
 """
 from __future__ import annotations
@@ -33,8 +34,9 @@ from .safetensors_io import SafetensorsFile, resolve_shards
 class TensorSpec:
     name: str                 # checkpoint name, e.g. model.layers.0.self_attn.q_proj.weight
     shape: Tuple[int, ...]
-    role: str = "matrix"      # "matrix" | "embedding" | "norm" | "bias" | "table" (integer)
+    role: str = "matrix"      # "matrix" | "embedding" | "norm" | "bias" | "coefficient" (kept float) | "table" (integer)
     fan_in: Optional[int] = None
+    init: Optional[str] = None   # how random weights draw a coefficient: "one", "mean", "identity", "fraction"
 
 
 class WeightsError(ValueError):
@@ -58,7 +60,7 @@ class UnexpectedTensorsWarning(UserWarning):
 
 
 def kept_dtype(role: str, model_dtype: torch.dtype) -> torch.dtype:
-    if role == "norm":
+    if role in ("norm", "coefficient"):
         return torch.float32
     if role == "table":
         return torch.int32

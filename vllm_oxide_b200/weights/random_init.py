@@ -4,7 +4,7 @@ The reference has no random-weights mode (its tests inject hash maps,
 vllm-oxide crates/vllm-oxide/src/layers/linear.rs:187-190).  Every tensor gets its own
 generator, seeded from (seed, tensor name), so the values do not depend on the order in
 which tensors are made.  Scheme "fan_in": embeddings N(0,1), matrices N(0, 1/fan_in);
-scheme "0.02": both N(0, 0.02^2); norm weights 1 + 0.1*N(0,1) in either.
+scheme "0.02": both N(0, 0.02^2); norm weights 1 + 0.1*N(0,1) in either; coefficients by their `init`.
 """
 from __future__ import annotations
 
@@ -29,7 +29,17 @@ def random_tensor(spec: TensorSpec, seed: int, scheme: str, device, dtype: torch
     if spec.role == "table":
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     x = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32)
-    if spec.role == "norm":
+    if spec.role == "coefficient":
+        # small learned numbers that must keep a random model tame: weights of a mean, an identity with noise, numbers in (0, 1)
+        if spec.init == "mean":
+            x = (1.0 + 0.1 * x) / max(1, spec.shape[-1])
+        elif spec.init == "identity":
+            x = torch.eye(spec.shape[-1], device=device, dtype=torch.float32) + 0.05 * x
+        elif spec.init == "fraction":
+            x = torch.sigmoid(x)
+        else:
+            x = 1.0 + 0.1 * x
+    elif spec.role == "norm":
         x = 1.0 + 0.1 * x
     elif spec.role == "bias":
         x = 0.02 * x
