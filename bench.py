@@ -18,6 +18,13 @@ of 8 requests whose context starts at 2,048 tokens, and prints ONE JSON line:
 The cache that the decode steps read was written by a real prefill of random prompts.  Every timed step reads 15 GB of weights, far more than the 126 MB L2, so nothing stays cached
 between iterations.  Peaks come from MEASURED_PEAKS.json beside this file when present.
 
+    python bench.py --workload tofilorn [--sizes 2048,4096]
+
+measures the Tofilorn design (residual streams, minGRU, HGRN2, latent attention) at layer sizes of 1B- and 8B-class
+models beside Qwen3 at the same width, depth and feed-forward size: one 2,048-token prompt in one step, decode at batch 8
+and 64 from a 2,048-token context (CUDA graphs), and, from an eager engine with the per-kernel timers on, the time of each
+of this package's kernels in those steps with the bytes it must move against the copy bandwidth.
+
     python bench.py --workload serving-0.6b | mixed-32b
 
 runs one of the two other workloads instead (whole requests through LLM.generate, wall clock, a JSON line of its
@@ -181,6 +188,28 @@ def decode_run(llm, batch, steps, warmup, start_ctx):
     return ms, launches, mean_ctx
 
 
+def decode_kernel_times(llm, batch, steps, start_ctx):
+    """{kernel: milliseconds a step} of this package's kernels in decode steps of an eager engine with the kernel timers on
+    (the prompts that fill the cache are not counted)."""
+    import torch
+    from vllm_oxide_b200 import host, kernels
+    mgr, core = llm.cache.manager, llm.core
+    ids = list(range(30_000, 30_000 + batch))
+    for rid in ids:
+        assert mgr.add_request(rid) and mgr.ensure(rid, 0, start_ctx)
+    fill_cache(llm, ids, start_ctx, seed=batch)
+    for i in range(3 + steps):
+        if i == 3:
+            kernels.kernel_timer_report()
+        for rid in ids:
+            assert mgr.ensure(rid, start_ctx + i, 1)
+        core.run([host.BatchEntry(rid, start_ctx + i, [1 + i], [0]) for rid in ids])
+    times = {k: round(v[1] / steps, 4) for k, v in sorted(kernels.kernel_timer_report().items())}
+    for rid in ids:
+        mgr.free_request(rid)
+    return times
+
+
 def e2e_run(llm, batch, steps, warmup):
     """The same metric through the public calls: prompts of 2,048 host token ids in, tokens out each step.
     Returns (tokens a second, host-to-device bytes a step, device-to-host bytes a step, milliseconds a step)."""
@@ -306,6 +335,91 @@ def workload_run(name: str, pk=None) -> dict:
                    "pool_pages": w["options"]["num_kv_blocks"], "block_size": w["options"]["block_size"]}}
 
 
+def tofilorn_config(width: int, layers: int) -> dict:
+    """Layer sizes of a real model of this width: a block of four layers (latent attention, minGRU, HGRN2, latent attention that
+    borrows the first one's keys), each with a gated feed-forward of three times the width, over four residual streams."""
+    heads = width // 128
+    rot = {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    att = lambda src: dict(heads=heads, dim=128, rot_dim=64, vdim=128, q_rank=3 * width // 8, kv_rank=192, scale=192 ** -0.5,
+                           mask={"size": 1024}, rot=rot, **({} if src is None else {"kv_from": src}))
+    mlp = {"kind": "dense", "ff": 3 * width}
+    out = []
+    for i in range(0, layers, 4):
+        out += [{"type": "latent_attention", "mixer": att(None), "mlp": mlp}, {"type": "mingru", "mixer": {"width": 2 * width}, "mlp": mlp},
+                {"type": "hgrn2", "mixer": {"heads": heads, "dim": 128, "vdim": 128}, "mlp": mlp},
+                {"type": "latent_attention", "mixer": att(i), "mlp": mlp}]
+    return {"architecture": "Tofilorn", "vocab": 32768, "width": width, "streams": 4, "norm": {"eps": 1e-6}, "layers": out[:layers]}
+
+
+def tofilorn_kernel_bytes(cfg: dict, T: int) -> dict:
+    """Bytes that each of the design's own kernels must move in a step of T tokens, summed over the layers (weights aside,
+    which T tokens share): what its time is held against."""
+    D, S = cfg["width"], cfg.get("streams", 1)
+    b = {"stream_step": 0, "mingru_scan": 0, "hgrn2_scan": 0, "latent_prep": 0, "head_linear": 0, "latent_query_rotate": 0}
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        subs = 2 if l["mlp"] else 1
+        b["stream_step"] += subs * T * (2 * S * D * 4 + 2 * D * 2)                # streams read and written, y in, normed out
+        if l["type"] == "mingru":
+            b["mingru_scan"] += T * 4 * m["width"] * 2
+        elif l["type"] == "hgrn2":
+            b["hgrn2_scan"] += T * m["heads"] * (2 * m["dim"] + 2 * m["vdim"]) * 2
+        else:
+            row = (m["kv_rank"] + m["rot_dim"] + 15) // 16 * 16
+            b["latent_prep"] += T * (2 * m["q_rank"] + (0 if "kv_from" in m else 2 * row)) * 2
+            b["latent_query_rotate"] += T * m["heads"] * 2 * m["rot_dim"] * 2
+            b["head_linear"] += (T * m["heads"] * (m["dim"] + 2 * row + m["vdim"]) + 2 * m["heads"] * m["kv_rank"] * (m["dim"] + m["vdim"])) * 2
+    return b
+
+
+def tofilorn_run(widths, pk=None, layers: int = 16) -> dict:
+    import torch
+    from vllm_oxide_b200 import LLM, EngineOptions, kernels
+    pk = pk or peaks()
+    out = {"metric": "tokens/s, Tofilorn beside Qwen3 at equal layer sizes", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+           "data": "synthetic token ids, seeded random weights", "peaks": pk, "sizes": {}}
+    for width in widths:
+        models = {"tofilorn": tofilorn_config(width, layers),
+                  "qwen3": dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=width // 128,
+                                num_key_value_heads=8, intermediate_size=3 * width, vocab_size=32768, max_position_embeddings=8192)}
+        rec = {}
+        for name, cfg in models.items():
+            r = {}
+            for eager in (False, True):
+                opts = EngineOptions(max_model_len=CONTEXT, block_size=BLOCK, num_kv_blocks=64 * 10 + 16, max_num_seqs=64,
+                                     max_num_batched_tokens=8192, dtype="bfloat16", enforce_eager=eager)
+                llm = LLM.from_config(cfg, opts, seed=0, init_scheme="0.02")
+                if not eager:
+                    r["weight_gb"] = round(llm.model.weight_bytes() / 1e9, 3)
+                    ms = prefill_run(llm, PROMPT_LEN)
+                    r["prefill_2048"] = {"ms": round(ms, 3), "tokens_per_s": round(PROMPT_LEN * 1e3 / ms)}
+                    for batch in (8, 64):
+                        ms, launches, _ = decode_run(llm, batch, 32, 4, PROMPT_LEN)
+                        r[f"decode_batch{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch * 1e3 / ms), "launches": launches // 32}
+                else:
+                    # this package's kernels one by one (library products are not among them), milliseconds a step
+                    kernels.enable_kernel_timers(True)
+                    prefill_run(llm, PROMPT_LEN, reps=1, warmup=1)
+                    kernels.kernel_timer_report()
+                    prefill_run(llm, PROMPT_LEN, reps=1, warmup=0)
+                    r["prefill_2048"]["own_kernels_ms"] = {k: round(v[1], 4) for k, v in sorted(kernels.kernel_timer_report().items())}
+                    r["decode_batch8"]["own_kernels_ms"] = decode_kernel_times(llm, 8, 8, PROMPT_LEN)
+                    kernels.enable_kernel_timers(False)
+                del llm
+                torch.cuda.empty_cache()
+            if name == "tofilorn":
+                for key, T in (("prefill_2048", PROMPT_LEN), ("decode_batch8", 8)):
+                    ms, by = r[key]["own_kernels_ms"], tofilorn_kernel_bytes(cfg, T)
+                    r[key]["own_kernels_frac_of_copy"] = {k: round(by[k] / (ms[k] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                                                          for k in by if ms.get(k)}
+            rec[name] = r
+        out["sizes"][str(width)] = rec
+    out["value"] = out["sizes"][str(widths[0])]["tofilorn"]["decode_batch8"]["tokens_per_s"]
+    out["config"] = {"layers": layers, "widths": list(widths), "prompt": PROMPT_LEN, "block_size": BLOCK,
+                     "l2": "weights of a step exceed L2 at every size"}
+    return out
+
+
 def attention_kernels_run(pk) -> dict:
     """The attention kernels alone.  Prefill: Qwen3-8B head shapes, one prompt of 2,048 and of 8,192 tokens, the device
     time of a launch (CUDA events around a graph of 20 launches, so the host's share of a launch is not in it).
@@ -398,7 +512,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (reported)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None, help="another workload instead of the default run")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["tofilorn"], default=None,
+                    help="another workload instead of the default run")
+    ap.add_argument("--sizes", default="2048,4096", help="--workload tofilorn: the widths to measure")
     ap.add_argument("--only", choices=["decode", "prefill", "attention"], default=None,
                     help="run one phase and print its time only (for short profiler captures)")
     args = ap.parse_args()
@@ -409,6 +525,9 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (use --gpus 1)")
         return 2
+    if args.workload == "tofilorn":
+        print(json.dumps(tofilorn_run([int(w) for w in args.sizes.split(",")])))
+        return 0
     if args.workload:
         print(json.dumps(workload_run(args.workload)))
         return 0

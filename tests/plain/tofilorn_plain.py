@@ -70,13 +70,15 @@ def rotation_frequencies(rot, dt):
 
 
 def rotate_pairs(x, pos, w, amp):
-    """x [..., n, 2m]: neighbours (2i, 2i+1) turned by the angle pos * w_i, both scaled by amp."""
+    """x [..., n, d]: among the first 2 len(w) elements, neighbours (2i, 2i+1) are turned by the angle pos * w_i and
+    scaled by amp; what lies behind them passes unchanged."""
     ang = pos.to(w.dtype)[:, None] * w[None, :]
     c, s = torch.cos(ang) * amp, torch.sin(ang) * amp
-    a, b = x[..., 0::2], x[..., 1::2]
-    out = torch.empty_like(x)
-    out[..., 0::2] = a * c - b * s
-    out[..., 1::2] = b * c + a * s
+    m = 2 * w.shape[0]
+    a, b = x[..., 0:m:2], x[..., 1:m:2]
+    out = x.clone()
+    out[..., 0:m:2] = a * c - b * s
+    out[..., 1:m:2] = b * c + a * s
     return out
 
 
@@ -130,7 +132,7 @@ def latent_keys(h, W, p, m, eps, pos):
 def latent_attention(h, W, p, m, eps, pos, kept):
     """Attention with keys and values expanded per head from a shared latent.  Queries: cq = norm(Wdq h), q = Wuq cq,
     per head [dim plain | rot_dim rotated].  Per head: plain key Wuk c, value Wuv c; score = (q_plain . k_plain +
-    q_rot . k_rot) * scale; position i sees j with 0 <= i - j < window; softmax; Wo on the heads side by side.
+    q_rot . k_rot) * scale; position i sees j with 0 <= i - j (< window, if there is one); softmax; Wo on the heads side by side.
     `kept` = (c, k_rot) of this layer or of the layer it borrows from."""
     nh, dk, dr, dv = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"])
     n = h.shape[0]
@@ -143,7 +145,9 @@ def latent_attention(h, W, p, m, eps, pos, kept):
     v = (c @ W[p + "uv"].T).reshape(n, nh, dv)
     score = (torch.einsum("ihd,jhd->hij", q[:, :, :dk], k) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * float(m["scale"])
     dist = pos[:, None] - pos[None, :]
-    seen = (dist >= 0) & (dist < int(m["mask"]["size"]))
+    seen = dist >= 0
+    if m.get("mask"):
+        seen &= dist < int(m["mask"]["size"])
     score = score.masked_fill(~seen[None], float("-inf"))
     o = torch.einsum("hij,jhd->ihd", torch.softmax(score, -1), v)
     return o.reshape(n, nh * dv) @ W[p + "o"].T

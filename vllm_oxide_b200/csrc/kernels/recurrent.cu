@@ -13,70 +13,136 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-
 // ---------------------------------------------------------------- minGRU
 // zxg [tokens, 3W]: pre-activations of the gate z, of the candidate u and of the output gate g (no bias yet).
 //   z = sigmoid(z + bz);  c = u + bx;  c = c >= 0 ? c + 1/2 : sigmoid(c);  s = (1 - z) s + z c;  out = s * silu(g)
-// One thread per (request, channel); neighbouring threads read neighbouring channels.
+// A block owns 32 channels of one request; neighbouring threads read neighbouring channels.  With NCH > 1 the request's
+// tokens of this step are cut into NCH ranges, one per thread row: every row first folds its range into (A, B) with
+// s_end = A s_start + B, the rows' starts follow from the state and the (A, B) before them, and a second walk writes
+// the outputs.  A recurrence is a chain: without the cut a prompt of thousands of tokens runs on a thread per channel.
+// The cut changes where a channel's additions are rounded, never what is computed.
+struct GruStep { float z, c, g; };
+
 template <typename T>
-__global__ void mingru_scan_kernel(const T* zxg, const T* __restrict__ bz, const T* __restrict__ bx, float* state,
-                                   const int* __restrict__ cu_q, const int* __restrict__ state_slots, T* out, int W,
-                                   int num_slots, int* err) {
+__device__ __forceinline__ GruStep gru_step(const T* row, int c, int W, float biasz, float biasx) {
+  GruStep r;
+  r.z = sigmoid_f(to_f<T>(row[c]) + biasz);
+  const float u = to_f<T>(row[W + c]) + biasx;
+  r.c = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+  r.g = to_f<T>(row[2 * W + c]);
+  return r;
+}
+
+template <typename T, int NCH>
+__global__ void __launch_bounds__(32 * NCH)
+mingru_scan_kernel(const T* zxg, const T* __restrict__ bz, const T* __restrict__ bx, float* state,
+                   const int* __restrict__ cu_q, const int* __restrict__ state_slots, T* out, int W,
+                   int num_slots, int* err) {
+  __shared__ float As[NCH][32], Bs[NCH][32];
   pdl_launch_dependents();
-  const int b = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y, lane = threadIdx.x, ch = threadIdx.y;
+  const int c = min(blockIdx.x * 32 + lane, W - 1);
+  const bool live = blockIdx.x * 32 + lane < W;
   const int t0 = cu_q[b], t1 = cu_q[b + 1];
   const int slot = state_slots[b];
-  const float biasz = c < W ? to_f<T>(bz[c]) : 0.f, biasx = c < W ? to_f<T>(bx[c]) : 0.f;
+  const float biasz = to_f<T>(bz[c]), biasx = to_f<T>(bx[c]);
   pdl_wait();
-  if (c >= W || t1 <= t0) return;
+  if (t1 <= t0) return;
   if (slot < 0 || slot >= num_slots) {
-    atomicOr(err, VOB_ERR_SLOT);
+    if (threadIdx.x == 0 && ch == 0) atomicOr(err, VOB_ERR_SLOT);
     return;
   }
+  const int per = (t1 - t0 + NCH - 1) / NCH;
+  const int lo = min(t1, t0 + ch * per), hi = min(t1, lo + per);
   float s = state[(size_t)slot * W + c];
+  if (NCH > 1) {
+    float A = 1.f, B = 0.f;
 #pragma unroll 4
-  for (int t = t0; t < t1; ++t) {
-    const T* row = zxg + (size_t)t * 3 * W;
-    const float z = sigmoid_f(to_f<T>(row[c]) + biasz);
-    const float u = to_f<T>(row[W + c]) + biasx;
-    const float g = to_f<T>(row[2 * W + c]);
-    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-    s = fmaf(z, cand, (1.f - z) * s);
-    out[(size_t)t * W + c] = from_f<T>(s * (g * sigmoid_f(g)));
+    for (int t = lo; t < hi; ++t) {
+      const GruStep g = gru_step<T>(zxg + (size_t)t * 3 * W, c, W, biasz, biasx);
+      A *= 1.f - g.z;
+      B = fmaf(g.z, g.c, (1.f - g.z) * B);
+    }
+    As[ch][lane] = A;
+    Bs[ch][lane] = B;
+    __syncthreads();
+    for (int k = 0; k < ch; ++k) s = fmaf(As[k][lane], s, Bs[k][lane]);
   }
-  state[(size_t)slot * W + c] = s;
+  // four tokens at a time: their loads are issued before the first store (the compiler cannot know that `out` is
+  // another buffer, and would otherwise wait for every store before the next token's loads)
+  int t = lo;
+  for (; t + 4 <= hi; t += 4) {
+    GruStep g[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) g[k] = gru_step<T>(zxg + (size_t)(t + k) * 3 * W, c, W, biasz, biasx);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      s = fmaf(g[k].z, g[k].c, (1.f - g[k].z) * s);
+      if (live) out[(size_t)(t + k) * W + c] = from_f<T>(s * (g[k].g * sigmoid_f(g[k].g)));
+    }
+  }
+  for (; t < hi; ++t) {
+    const GruStep g = gru_step<T>(zxg + (size_t)t * 3 * W, c, W, biasz, biasx);
+    s = fmaf(g.z, g.c, (1.f - g.z) * s);
+    if (live) out[(size_t)t * W + c] = from_f<T>(s * (g.g * sigmoid_f(g.g)));
+  }
+  if (ch == NCH - 1 && live) state[(size_t)slot * W + c] = s;
 }
 
 // ---------------------------------------------------------------- HGRN2
 // qfv [tokens, heads*dk | heads*dk | heads*dv]: pre-activations of q and of the forget gate, and the values.
 //   q = silu(q);  f = l + (1 - l) sigmoid(f + bf);  M = diag(f) M + (1 - f) v^T;  o = M^T q;  out = o / rms(o) * w
-// A block owns (request, head) or a range of its value columns; thread j keeps column j of M (dk floats) in registers, so
-// a token costs dk multiply-adds a thread and no exchange between threads.  The gates of HG_TT tokens are made by the
-// whole block at once and parked in shared memory.  FUSE: the block holds all dv columns of the head and also takes
-// the norm over them; otherwise o leaves in float and head_gain_norm_kernel follows.
-constexpr int HG_TT = 8;
+// Column j of a head's state M (dk floats) is shared by PARTS neighbouring lanes, R rows each, in registers: a token costs
+// a thread R multiply-adds twice, and the lanes of a column add their parts of o by shuffles.  The gates of HG_TT tokens are
+// made by the whole block at once and parked in shared memory (rows padded so that the PARTS lanes of a column read
+// different banks).  FUSE: the block holds all dv columns of the head and also takes the norm over them (decoding: one
+// launch); otherwise a block holds as many columns as 128 threads cover, so that a long portion of one request spreads
+// over more blocks, o leaves in float and head_gain_norm_kernel follows.  Both give the same numbers: an element's
+// chain of operations depends on (R, PARTS) alone, and those follow from dk.
+//
+// A long portion is also cut along the tokens (`chunks` > 1, three launches): MODE 1 walks every range from a zero state
+// and leaves its end state L and the product F of its gates; hgrn2_join_kernel goes through the ranges in order,
+// M_start(c+1) = diag(F_c) M_start(c) + L_c, leaves every range's start where its L was and the last state in the
+// slot; MODE 2 walks the ranges again from their starts and writes the outputs.  Twice the arithmetic, on as many more
+// blocks as there are ranges.  MODE 0 is the walk from the slot's state to the slot's state in one launch.
+constexpr int HG_TT = 16;
 
-template <typename T, int R, bool FUSE>
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ int hg_pad(int i) { return i + (i >> 5); }
+
+template <typename T, int R, int PARTS, bool FUSE, int MODE>
+__global__ void __launch_bounds__(FUSE ? (R > 32 ? 256 : 512) : 128)
 hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restrict__ lower, const float* __restrict__ nw,
                   float* state, const int* __restrict__ cu_q, const int* __restrict__ state_slots, T* out, float* raw,
-                  int heads, int dk, int dv, int col_blocks, float eps, int num_slots, int* err) {
+                  float* ends, float* gates, int heads, int dk, int dv, int col_blocks, float eps, int num_slots, int* err) {
   extern __shared__ float sm[];
-  float* qs = sm;                   // [HG_TT][dk]
-  float* fs = qs + HG_TT * dk;      // [HG_TT][dk]
-  float* os = fs + HG_TT * dk;      // [HG_TT][blockDim.x]
+  const int gate_row = hg_pad(R * PARTS) + 1;
+  const int cols = blockDim.x / PARTS;
+  float* qs = sm;                        // [HG_TT][gate_row]
+  float* fs = qs + HG_TT * gate_row;     // [HG_TT][gate_row]
+  float* vs = fs + HG_TT * gate_row;     // [HG_TT][cols]
+  float* os = vs + HG_TT * cols;         // [HG_TT][cols]  (FUSE)
   pdl_launch_dependents();
-  const int h = blockIdx.x / col_blocks, j = (blockIdx.x % col_blocks) * blockDim.x + threadIdx.x;
-  const int b = blockIdx.y;
-  const int t0 = cu_q[b], t1 = cu_q[b + 1];
+  const int part = threadIdx.x % PARTS, jj = threadIdx.x / PARTS;
+  const int h = blockIdx.x / col_blocks, cb = blockIdx.x % col_blocks, j = cb * cols + jj;
+  const int b = blockIdx.y, chunk = blockIdx.z, chunks = gridDim.z;
+  const int q0 = cu_q[b], q1 = cu_q[b + 1];
   const int slot = state_slots[b];
   pdl_wait();
-  if (t1 <= t0) return;
+  if (q1 <= q0) return;
   if (slot < 0 || slot >= num_slots) {
     if (threadIdx.x == 0) atomicOr(err, VOB_ERR_SLOT);
     return;
   }
+  const int per = (q1 - q0 + chunks - 1) / chunks;
+  const int t0 = min(q1, q0 + chunk * per), t1 = min(q1, t0 + per);
   const size_t width = (size_t)heads * (2 * dk + dv);
-  float* mine = state + (((size_t)slot * heads + h) * dk) * dv + j;
-  float M[R];
+  const int i0 = part * R;
+  float* mine = MODE == 0 ? state + (((size_t)slot * heads + h) * dk + i0) * dv + j
+                          : ends + ((((size_t)b * chunks + chunk) * heads + h) * dk + i0) * dv + j;
+  float M[R], F[MODE == 1 ? R : 1];
 #pragma unroll
-  for (int i = 0; i < R; ++i) M[i] = (i < dk && j < dv) ? mine[(size_t)i * dv] : 0.f;
+  for (int i = 0; i < R; ++i) M[i] = (MODE != 1 && i0 + i < dk && j < dv) ? mine[(size_t)i * dv] : 0.f;
+  if (MODE == 1) {
+#pragma unroll
+    for (int i = 0; i < R; ++i) F[MODE == 1 ? i : 0] = 1.f;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   for (int ts = t0; ts < t1; ts += HG_TT) {
     const int n = min(HG_TT, t1 - ts);
@@ -84,43 +150,82 @@ hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restric
       const int tt = idx / dk, i = idx % dk;
       const T* row = qfv + (size_t)(ts + tt) * width;
       const float qv = to_f<T>(row[h * dk + i]);
-      qs[tt * dk + i] = qv * sigmoid_f(qv);
+      qs[tt * gate_row + hg_pad(i)] = qv * sigmoid_f(qv);
       const float l = lower[h * dk + i];
-      fs[tt * dk + i] = l + (1.f - l) * sigmoid_f(to_f<T>(row[(heads + h) * dk + i]) + to_f<T>(bf[h * dk + i]));
+      fs[tt * gate_row + hg_pad(i)] = l + (1.f - l) * sigmoid_f(to_f<T>(row[(heads + h) * dk + i]) + to_f<T>(bf[h * dk + i]));
+    }
+    for (int idx = threadIdx.x; idx < n * cols; idx += blockDim.x) {
+      const int tt = idx / cols, c = idx % cols;
+      vs[idx] = cb * cols + c < dv ? to_f<T>(qfv[(size_t)(ts + tt) * width + (size_t)2 * heads * dk + h * dv + cb * cols + c]) : 0.f;
     }
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
       float o = 0.f;
-      if (j < dv) {
-        const float v = to_f<T>(qfv[(size_t)(ts + tt) * width + (size_t)2 * heads * dk + h * dv + j]);
+      const float v = vs[tt * cols + jj];
+      const float* fr = fs + tt * gate_row + hg_pad(i0);
+      const float* qr = qs + tt * gate_row + hg_pad(i0);
 #pragma unroll
-        for (int i = 0; i < R; ++i)
-          if (i < dk) {
-            const float f = fs[tt * dk + i];
-            M[i] = fmaf(f, M[i], (1.f - f) * v);
-            o = fmaf(M[i], qs[tt * dk + i], o);
-          }
-        if (!FUSE) raw[(size_t)(ts + tt) * heads * dv + h * dv + j] = o;
+      for (int i = 0; i < R; ++i)
+        if (i0 + i < dk) {
+          const float f = fr[i + (i >> 5)];      // hg_pad(i0 + i): i0 is a multiple of 32 wherever R exceeds it
+          M[i] = fmaf(f, M[i], (1.f - f) * v);
+          if (MODE == 1) F[MODE == 1 ? i : 0] *= f;
+          else o = fmaf(M[i], qr[i + (i >> 5)], o);
+        }
+      if (MODE != 1) {
+#pragma unroll
+        for (int d = 1; d < PARTS; d <<= 1) o += __shfl_xor_sync(0xffffffffu, o, d);
+        if (FUSE) {
+          if (part == 0) os[tt * cols + jj] = o;
+        } else if (part == 0 && j < dv) {
+          raw[(size_t)(ts + tt) * heads * dv + h * dv + j] = o;
+        }
       }
-      if (FUSE) os[tt * blockDim.x + threadIdx.x] = o;
     }
     __syncthreads();
-    if (FUSE) {
+    if (FUSE && MODE != 1) {
       for (int tt = warp; tt < n; tt += nwarps) {
         float ss = 0.f;
-        for (int c = lane; c < dv; c += 32) ss += os[tt * blockDim.x + c] * os[tt * blockDim.x + c];
+        for (int c = lane; c < dv; c += 32) ss += os[tt * cols + c] * os[tt * cols + c];
         const float denom = sqrtf(warp_sum(ss) / (float)dv + eps);
         for (int c = lane; c < dv; c += 32)
-          out[(size_t)(ts + tt) * heads * dv + h * dv + c] = from_f<T>(os[tt * blockDim.x + c] / denom * nw[c]);
+          out[(size_t)(ts + tt) * heads * dv + h * dv + c] = from_f<T>(os[tt * cols + c] / denom * nw[c]);
       }
       __syncthreads();
     }
   }
+  if (MODE == 2) return;
   if (j < dv) {
 #pragma unroll
     for (int i = 0; i < R; ++i)
-      if (i < dk) mine[(size_t)i * dv] = M[i];
+      if (i0 + i < dk) mine[(size_t)i * dv] = M[i];
   }
+  if (MODE == 1 && j == 0) {
+    float* g = gates + (((size_t)b * chunks + chunk) * heads + h) * dk + i0;
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      if (i0 + i < dk) g[i] = F[MODE == 1 ? i : 0];
+  }
+}
+
+// One thread per element of a request's state: through the ranges in order, start(c) takes the place of L_c.
+__global__ void hgrn2_join_kernel(float* state, float* ends, const float* gates, const int* __restrict__ cu_q,
+                                  const int* __restrict__ state_slots, int chunks, int heads, int dk, int dv, int num_slots) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.y;
+  const long e = (long)blockIdx.x * blockDim.x + threadIdx.x, per = (long)heads * dk * dv;
+  const int slot = state_slots[b];
+  if (e >= per || cu_q[b + 1] <= cu_q[b] || slot < 0 || slot >= num_slots) return;
+  const long row = e / dv;      // (head, i)
+  float M = state[(size_t)slot * per + e];
+  for (int c = 0; c < chunks; ++c) {
+    float* L = ends + ((size_t)b * chunks + c) * per + e;
+    const float l = *L, f = gates[((size_t)b * chunks + c) * heads * dk + row];
+    *L = M;
+    M = fmaf(f, M, l);
+  }
+  state[(size_t)slot * per + e] = M;
 }
 
 // out[t, h, :] = raw[t, h, :] / sqrt(mean(raw[t, h, :]^2) + eps) * w; one warp per (token, head).
@@ -137,35 +242,61 @@ __global__ void head_gain_norm_kernel(const float* raw, const float* __restrict_
   for (int c = lane; c < dv; c += 32) out[(size_t)row * dv + c] = from_f<T>(x[c] / denom * w[c]);
 }
 
-template <typename T, int R>
+template <typename T, int R, int PARTS, int MODE>
 int launch_hgrn2(const void* qfv, const void* bf, const float* lower, const float* nw, float* state, const int* cu_q,
-                 const int* state_slots, void* out, float* raw, int B, int heads, int dk, int dv, float eps, int num_slots,
-                 int* err, cudaStream_t stream) {
-  const bool fuse = dv <= 128;
-  const int threads = fuse ? (dv + 31) / 32 * 32 : 128;
-  const int col_blocks = fuse ? 1 : (dv + 127) / 128;
-  const size_t smem = ((size_t)2 * HG_TT * dk + (size_t)HG_TT * threads) * sizeof(float);
-  dim3 grid(heads * col_blocks, B);
+                 const int* state_slots, void* out, float* raw, float* ends, float* gates, int B, int chunks, int heads, int dk,
+                 int dv, float eps, int num_slots, int fuse, int* err, cudaStream_t stream) {
+  const int gate_row = R * PARTS + (R * PARTS) / 32 + 1;
+  const int threads = fuse ? (dv * PARTS + 31) / 32 * 32 : 128;
+  const int cols = threads / PARTS;
+  const int col_blocks = fuse ? 1 : (dv + cols - 1) / cols;
+  const size_t smem = ((size_t)2 * HG_TT * gate_row + (fuse ? 2 : 1) * (size_t)HG_TT * cols) * sizeof(float);
+  dim3 grid(heads * col_blocks, B, chunks);
   if (fuse)
-    return launch_kernel(hgrn2_scan_kernel<T, R, true>, grid, dim3(threads), smem, stream, (const T*)qfv, (const T*)bf, lower, nw,
-                         state, cu_q, state_slots, (T*)out, raw, heads, dk, dv, col_blocks, eps, num_slots, err);
-  return launch_kernel(hgrn2_scan_kernel<T, R, false>, grid, dim3(threads), smem, stream, (const T*)qfv, (const T*)bf, lower, nw,
-                       state, cu_q, state_slots, (T*)out, raw, heads, dk, dv, col_blocks, eps, num_slots, err);
+    return launch_kernel(hgrn2_scan_kernel<T, R, PARTS, true, 0>, grid, dim3(threads), smem, stream, (const T*)qfv, (const T*)bf,
+                         lower, nw, state, cu_q, state_slots, (T*)out, raw, ends, gates, heads, dk, dv, col_blocks, eps, num_slots, err);
+  return launch_kernel(hgrn2_scan_kernel<T, R, PARTS, false, MODE>, grid, dim3(threads), smem, stream, (const T*)qfv, (const T*)bf,
+                       lower, nw, state, cu_q, state_slots, (T*)out, raw, ends, gates, heads, dk, dv, col_blocks, eps, num_slots, err);
+}
+
+// rows of the state a thread keeps, and lanes that share a column: from dk alone
+inline int hgrn2_parts(int dk) { return dk <= 32 ? 1 : dk <= 64 ? 2 : 4; }
+
+template <typename T, int MODE>
+int dispatch_hgrn2_mode(const void* qfv, const void* bf, const float* lower, const float* nw, float* state, const int* cu_q,
+                        const int* state_slots, void* out, float* raw, float* ends, float* gates, int B, int chunks, int heads,
+                        int dk, int dv, float eps, int num_slots, int fuse, int* err, cudaStream_t stream) {
+#define VOB_HG(RR, PP) return launch_hgrn2<T, RR, PP, MODE>(qfv, bf, lower, nw, state, cu_q, state_slots, out, raw, ends, gates, B, chunks, heads, dk, dv, eps, num_slots, fuse, err, stream)
+  if (dk <= 16) VOB_HG(16, 1);
+  if (dk <= 32) VOB_HG(32, 1);
+  if (dk <= 64) VOB_HG(32, 2);
+  if (dk <= 128) VOB_HG(32, 4);
+  VOB_HG(64, 4);
+#undef VOB_HG
 }
 
 template <typename T>
 int dispatch_hgrn2(const void* qfv, const void* bf, const float* lower, const float* nw, float* state, const int* cu_q,
-                   const int* state_slots, void* out, float* raw, int Tn, int B, int heads, int dk, int dv, float eps,
-                   int num_slots, int* err, cudaStream_t stream) {
+                   const int* state_slots, void* out, float* raw, float* scratch, int Tn, int B, int chunks, int heads, int dk,
+                   int dv, float eps, int num_slots, int fuse, int* err, cudaStream_t stream) {
   int code;
-#define VOB_HG(RR) code = launch_hgrn2<T, RR>(qfv, bf, lower, nw, state, cu_q, state_slots, out, raw, B, heads, dk, dv, eps, num_slots, err, stream)
-  if (dk <= 16) VOB_HG(16);
-  else if (dk <= 32) VOB_HG(32);
-  else if (dk <= 64) VOB_HG(64);
-  else if (dk <= 128) VOB_HG(128);
-  else VOB_HG(256);
-#undef VOB_HG
-  if (code != 0 || dv <= 128) return code;
+  if (chunks <= 1) {
+    code = dispatch_hgrn2_mode<T, 0>(qfv, bf, lower, nw, state, cu_q, state_slots, out, raw, nullptr, nullptr, B, 1, heads, dk, dv,
+                                     eps, num_slots, fuse, err, stream);
+  } else {
+    float* ends = scratch;
+    float* gates = scratch + (size_t)B * chunks * heads * dk * dv;
+    code = dispatch_hgrn2_mode<T, 1>(qfv, bf, lower, nw, state, cu_q, state_slots, out, raw, ends, gates, B, chunks, heads, dk, dv,
+                                     eps, num_slots, 0, err, stream);
+    if (code != 0) return code;
+    const long per = (long)heads * dk * dv;
+    code = launch_kernel(hgrn2_join_kernel, dim3((unsigned)((per + 255) / 256), B), dim3(256), 0, stream, state, ends,
+                         (const float*)gates, cu_q, state_slots, chunks, heads, dk, dv, num_slots);
+    if (code != 0) return code;
+    code = dispatch_hgrn2_mode<T, 2>(qfv, bf, lower, nw, state, cu_q, state_slots, out, raw, ends, gates, B, chunks, heads, dk, dv,
+                                     eps, num_slots, 0, err, stream);
+  }
+  if (code != 0 || fuse) return code;
   const int rows = Tn * heads;
   return launch_kernel(head_gain_norm_kernel<T>, dim3((rows + 3) / 4), dim3(128), 0, stream, (const float*)raw, nw, (T*)out, rows, dv,
                        eps);
@@ -176,34 +307,49 @@ int dispatch_hgrn2(const void* qfv, const void* bf, const float* lower, const fl
 using namespace vob;
 
 // zxg [T, 3W], bz and bx [W] of the model's type; state float [num_slots, W]; cu_q [B+1]; state_slots [B]; out [T, W].
+// `chunks`: 1, 8 or 32 ranges that a request's tokens are cut into (more for longer portions).
 VOB_API int vob_mingru_scan(const void* zxg, const void* bz, const void* bx, float* state, const int* cu_q,
-                            const int* state_slots, void* out, int B, int W, int num_slots, int dtype, int* err,
+                            const int* state_slots, void* out, int B, int W, int num_slots, int chunks, int dtype, int* err,
                             cudaStream_t stream) {
   if (B <= 0 || W <= 0) return 0;
-  if (B > 65535) return VOB_UNSUPPORTED;
-  dim3 grid((W + 63) / 64, B);
-  if (dtype == VOB_F32)
-    return launch_kernel(mingru_scan_kernel<float>, grid, dim3(64), 0, stream, (const float*)zxg, (const float*)bz, (const float*)bx,
-                         state, cu_q, state_slots, (float*)out, W, num_slots, err);
-  if (dtype == VOB_BF16)
-    return launch_kernel(mingru_scan_kernel<__nv_bfloat16>, grid, dim3(64), 0, stream, (const __nv_bfloat16*)zxg,
-                         (const __nv_bfloat16*)bz, (const __nv_bfloat16*)bx, state, cu_q, state_slots, (__nv_bfloat16*)out, W,
-                         num_slots, err);
+  if (B > 65535 || (chunks != 1 && chunks != 8 && chunks != 32)) return VOB_UNSUPPORTED;
+  dim3 grid((W + 31) / 32, B), block(32, chunks);
+#define VOB_GRU(TT, NN) \
+  return launch_kernel(mingru_scan_kernel<TT, NN>, grid, block, 0, stream, (const TT*)zxg, (const TT*)bz, (const TT*)bx, state, cu_q, \
+                       state_slots, (TT*)out, W, num_slots, err)
+  if (dtype == VOB_F32) {
+    if (chunks == 1) VOB_GRU(float, 1);
+    if (chunks == 8) VOB_GRU(float, 8);
+    VOB_GRU(float, 32);
+  }
+  if (dtype == VOB_BF16) {
+    if (chunks == 1) VOB_GRU(__nv_bfloat16, 1);
+    if (chunks == 8) VOB_GRU(__nv_bfloat16, 8);
+    VOB_GRU(__nv_bfloat16, 32);
+  }
+#undef VOB_GRU
   return VOB_BAD_ARGUMENT;
 }
 
 // qfv [T, heads*(2 dk + dv)], bf [heads*dk] of the model's type; lower [heads*dk], nw [dv] float; state float
-// [num_slots, heads, dk, dv]; out [T, heads*dv]; raw: float [T, heads*dv], needed when dv > 128.
+// [num_slots, heads, dk, dv]; out [T, heads*dv].  `fuse`: one block a (request, head) that also takes the norm (it must
+// be able to hold the head: vob_hgrn2_can_fuse); else blocks of 128 threads and raw, float [T, heads*dv], in between.
+// `chunks` > 1 (not with fuse): ranges that a request's tokens are cut into, with scratch of
+// B * chunks * heads * dk * (dv + 1) floats.
+VOB_API int vob_hgrn2_can_fuse(int dk, int dv) { return dv * hgrn2_parts(dk) <= (dk > 128 ? 256 : 512) ? 1 : 0; }
+
 VOB_API int vob_hgrn2_scan(const void* qfv, const void* bf, const float* lower, const float* nw, float* state, const int* cu_q,
-                           const int* state_slots, void* out, float* raw, int T, int B, int heads, int dk, int dv, float eps,
-                           int num_slots, int dtype, int* err, cudaStream_t stream) {
+                           const int* state_slots, void* out, float* raw, float* scratch, int T, int B, int chunks, int heads,
+                           int dk, int dv, float eps, int num_slots, int fuse, int dtype, int* err, cudaStream_t stream) {
   if (B <= 0 || T <= 0) return 0;
-  if (heads <= 0 || dk <= 0 || dv <= 0 || dk > 256 || B > 65535 || (dv > 128 && !raw)) return VOB_UNSUPPORTED;
+  if (heads <= 0 || dk <= 0 || dv <= 0 || dk > 256 || B > 65535 || (!fuse && !raw) || (fuse && !vob_hgrn2_can_fuse(dk, dv)) ||
+      chunks < 1 || chunks > 64 || (chunks > 1 && (fuse || !scratch)))
+    return VOB_UNSUPPORTED;
   if (dtype == VOB_F32)
-    return dispatch_hgrn2<float>(qfv, bf, lower, nw, state, cu_q, state_slots, out, raw, T, B, heads, dk, dv, eps, num_slots, err,
-                                 stream);
+    return dispatch_hgrn2<float>(qfv, bf, lower, nw, state, cu_q, state_slots, out, raw, scratch, T, B, chunks, heads, dk, dv, eps,
+                                 num_slots, fuse, err, stream);
   if (dtype == VOB_BF16)
-    return dispatch_hgrn2<__nv_bfloat16>(qfv, bf, lower, nw, state, cu_q, state_slots, out, raw, T, B, heads, dk, dv, eps,
-                                         num_slots, err, stream);
+    return dispatch_hgrn2<__nv_bfloat16>(qfv, bf, lower, nw, state, cu_q, state_slots, out, raw, scratch, T, B, chunks, heads, dk,
+                                         dv, eps, num_slots, fuse, err, stream);
   return VOB_BAD_ARGUMENT;
 }

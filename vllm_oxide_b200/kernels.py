@@ -243,30 +243,47 @@ def stream_sum(streams, sums, num_streams: int, width: int) -> None:
     _check(lib().vob_stream_sum(_p(streams), _p(sums), sums.shape[0], num_streams, width, _stream()), "stream_sum")
 
 
-def mingru_scan(zxg, bias_z, bias_x, state, cu_q, state_slots, out, num_requests: int, err) -> None:
+def scan_chunks(num_tokens: int, num_requests: int) -> int:
+    """Ranges that a scan cuts a request's tokens of a step into, from the step's mean portion: 1 while decoding."""
+    mean = num_tokens / max(1, num_requests)
+    return 1 if mean <= 4 else (8 if mean <= 256 else 32)
+
+
+def mingru_scan(zxg, bias_z, bias_x, state, cu_q, state_slots, out, num_requests: int, err, chunks: int = 1) -> None:
     """The gated recurrence s = (1 - z) s + z * candidate over every request's tokens of this step, from and to its
-    state slot (float [slots, width]); zxg [tokens, 3 * width] holds the pre-activations z | candidate | output gate."""
+    state slot (float [slots, width]); zxg [tokens, 3 * width] holds the pre-activations z | candidate | output gate.
+    `chunks` (1, 8 or 32): ranges of a request's tokens that are folded side by side (see scan_chunks)."""
     _cuda(zxg, bias_z, bias_x, state, cu_q, state_slots, out)
     W = out.shape[1]
     assert zxg.is_contiguous() and out.is_contiguous() and zxg.shape[1] == 3 * W and state.dtype == torch.float32
     assert state.is_contiguous() and state.shape[1] == W and bias_z.dtype == zxg.dtype == bias_x.dtype == out.dtype
     _check(lib().vob_mingru_scan(_p(zxg), _p(bias_z), _p(bias_x), _p(state), _p(cu_q), _p(state_slots), _p(out),
-                                 num_requests, W, state.shape[0], _code(out.dtype), _p(err), _stream()), "mingru_scan")
+                                 num_requests, W, state.shape[0], int(chunks), _code(out.dtype), _p(err), _stream()),
+           "mingru_scan")
 
 
 def hgrn2_scan(qfv, bias_f, lower, norm_weight, state, cu_q, state_slots, out, num_requests: int, heads: int, dk: int,
-               dv: int, eps: float, err, raw=None) -> None:
+               dv: int, eps: float, err, raw=None, chunks: int = 1, scratch=None) -> None:
     """The matrix-state recurrence M = diag(f) M + (1 - f) v^T, o = M^T q, with the per-head norm of o, over every
-    request's tokens of this step; state float [slots, heads, dk, dv]; qfv [tokens, heads * (2 dk + dv)].  `raw`
-    (float [tokens, heads * dv]) is needed when dv > 128."""
+    request's tokens of this step; state float [slots, heads, dk, dv]; qfv [tokens, heads * (2 dk + dv)].  Without `raw`
+    one block a (request, head) does it all (decoding; the head must fit: hgrn2_can_fuse); with `raw` (float [tokens,
+    heads * dv]) a head's columns are spread over blocks and the norm is a second kernel (portions).  Same numbers.
+    `chunks` > 1 (with `raw`): a request's tokens are cut into that many ranges that are walked side by side, twice,
+    with a join in between; `scratch`: float, num_requests * chunks * heads * dk * (dv + 1) elements."""
     _cuda(qfv, bias_f, lower, norm_weight, state, cu_q, state_slots, out, raw)
     T = out.shape[0]
     assert qfv.is_contiguous() and out.is_contiguous() and qfv.shape[1] == heads * (2 * dk + dv) and out.shape[1] == heads * dv
     assert state.dtype == torch.float32 and state.is_contiguous() and state[0].numel() == heads * dk * dv
     assert lower.dtype == torch.float32 and norm_weight.dtype == torch.float32 and bias_f.dtype == qfv.dtype == out.dtype
+    assert chunks == 1 or (raw is not None and scratch is not None and scratch.dtype == torch.float32
+                           and scratch.numel() >= num_requests * chunks * heads * dk * (dv + 1))
     _check(lib().vob_hgrn2_scan(_p(qfv), _p(bias_f), _p(lower), _p(norm_weight), _p(state), _p(cu_q), _p(state_slots),
-                                _p(out), _p(raw), T, num_requests, heads, dk, dv, ctypes.c_float(eps), state.shape[0],
-                                _code(out.dtype), _p(err), _stream()), "hgrn2_scan")
+                                _p(out), _p(raw), _p(scratch), T, num_requests, int(chunks), heads, dk, dv, ctypes.c_float(eps),
+                                state.shape[0], int(raw is None), _code(out.dtype), _p(err), _stream()), "hgrn2_scan")
+
+
+def hgrn2_can_fuse(dk: int, dv: int) -> bool:
+    return bool(lib().vob_hgrn2_can_fuse(dk, dv))
 
 
 def latent_prep(down, wq, wkv, rule, positions, slots, cq, cache, num_tokens: int, q_rank: int, kv_rank: int, rot: int,

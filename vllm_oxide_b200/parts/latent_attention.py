@@ -37,6 +37,9 @@ from .base import NO_ROTATION, CacheSpec, Mixer, register_part
 from .linear import linear
 
 
+FAST_GROUP = 16     # query heads that the tensor-core attention kernels take for one key head
+
+
 class LatentAttention(Mixer):
     graph_safe = True
 
@@ -87,7 +90,8 @@ class LatentAttention(Mixer):
         self.wuv = tensors[p + "uv"].reshape(self.nh, self.dv, self.kv_rank).transpose(1, 2).contiguous()
         self.wo = tensors[p + "o"].contiguous()
         if self.wo.is_cuda:
-            self._pairs = kernels.decode_pairs_counter(self.wo.device)
+            # a counter for every group of heads that goes to the decode kernel on its own (see forward)
+            self._pairs = [kernels.decode_pairs_counter(self.wo.device) for _ in range(0, self.nh, FAST_GROUP)]
 
     def cache_spec(self) -> Optional[CacheSpec]:
         return None if self.borrow else CacheSpec(1, self.row, self.cache_window, tensors=1)
@@ -106,11 +110,19 @@ class LatentAttention(Mixer):
         qa = ctx.ws.get("latent_qa", T, nh * self.row, x.dtype)
         kernels.head_linear(q, nh * (self.dk + self.dr), self.dk + self.dr, self.wuk, qa, nh * self.row, self.row, T)
         kernels.latent_query_rotate(q, qa, self.rotation, ctx.positions, T, nh, self.dk, self.dr, self.kv_rank, self.row)
-        mixed = ctx.ws.get("latent_mixed", T, nh * self.row, x.dtype)
-        w = paged_attend(qa, nh * self.row, mixed, cache.k, cache.k, cache.group, ctx, T, nh, 1, self.row, self.window,
-                         self.scale, self._pairs, value_dim=self.kv_rank)
         heads = ctx.ws.get("latent_heads", T, nh * self.dv, x.dtype)
-        kernels.head_linear(mixed, nh * w, w, self.wuv, heads, nh * self.dv, self.dv, T)
+        # the tensor-core kernels take up to FAST_GROUP query heads for one key head: more heads go in groups, each with
+        # the same plane (the plain kernel takes them all at once)
+        fast = kernels.has_fast_attention(x.dtype, self.row, min(nh, FAST_GROUP))
+        step = min(nh, FAST_GROUP) if fast else nh
+        for k, h0 in enumerate(range(0, nh, step)):
+            n = min(step, nh - h0)
+            mixed = ctx.ws.get(f"latent_mixed{k}", T, n * self.row, x.dtype)
+            w = paged_attend(qa[:, h0 * self.row:(h0 + n) * self.row], nh * self.row, mixed, cache.k, cache.k, cache.group, ctx, T,
+                             n, 1, self.row, self.window, self.scale, self._pairs[k] if self._pairs else None,
+                             value_dim=self.kv_rank)
+            kernels.head_linear(mixed, n * w, w, self.wuv[h0:h0 + n], heads[:, h0 * self.dv:(h0 + n) * self.dv], nh * self.dv,
+                                self.dv, T)
         return linear(heads, self.wo, ctx.ws.get("mixer_proj", T, self.H, x.dtype), ctx)
 
 

@@ -52,7 +52,8 @@ class MinGRU(Mixer):
         T = x.shape[0]
         zxg = linear(x, self.wzxg, ctx.ws.get("mingru_zxg", T, 3 * self.W, x.dtype), ctx)
         gated = ctx.ws.get("mingru_out", T, self.W, x.dtype)
-        kernels.mingru_scan(zxg, self.bz, self.bx, state, ctx.cu_q, ctx.state_slots, gated, ctx.launch_requests, ctx.err)
+        kernels.mingru_scan(zxg, self.bz, self.bx, state, ctx.cu_q, ctx.state_slots, gated, ctx.launch_requests, ctx.err,
+                            chunks=kernels.scan_chunks(T, ctx.launch_requests))
         return linear(gated, self.wo, ctx.ws.get("mixer_proj", T, self.H, x.dtype), ctx)
 
 
@@ -87,9 +88,16 @@ class HGRN2(Mixer):
         width = self.nh * (2 * self.dk + self.dv)
         qfv = linear(x, self.wqfv, ctx.ws.get("hgrn2_qfv", T, width, x.dtype), ctx)
         out = ctx.ws.get("hgrn2_out", T, self.nh * self.dv, x.dtype)
-        raw = ctx.ws.get("hgrn2_raw", T, self.nh * self.dv, torch.float32) if self.dv > 128 else None
+        # decoding: one block a (request, head), norm included; portions: a head's columns over several blocks
+        fuse = kernels.hgrn2_can_fuse(self.dk, self.dv) and T <= 16 * ctx.launch_requests
+        raw = None if fuse else ctx.ws.get("hgrn2_raw", T, self.nh * self.dv, torch.float32)
+        # longer portions are also cut along the tokens (the mean portion decides, as for every scan)
+        B = ctx.launch_requests
+        chunks = 1 if fuse else min(kernels.scan_chunks(T, B), 16)
+        scratch = None if chunks == 1 else ctx.ws.get_flat("hgrn2_ranges", B * chunks * self.nh * self.dk * (self.dv + 1),
+                                                           torch.float32)
         kernels.hgrn2_scan(qfv, self.bf, self.lower, self.norm_weight, state, ctx.cu_q, ctx.state_slots, out,
-                           ctx.launch_requests, self.nh, self.dk, self.dv, self.eps, ctx.err, raw=raw)
+                           B, self.nh, self.dk, self.dv, self.eps, ctx.err, raw=raw, chunks=chunks, scratch=scratch)
         return linear(out, self.wo, ctx.ws.get("mixer_proj", T, self.H, x.dtype), ctx)
 
 

@@ -108,7 +108,7 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor]) -> None:
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"cannot store dtype {t.dtype} of tensor {name}")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""   # reshape: a single number has no axis to view
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)
