@@ -1,4 +1,4 @@
-"""vllm_oxide_b200: a small, whole, single-GPU inference engine for Qwen3 (dense) on B200 (sm_100a).
+"""vllm_oxide_b200: a small, whole, single-GPU inference engine for Qwen3 (dense) and Tofilorn on B200 (sm_100a).
 
     from vllm_oxide_b200 import LLM, EngineOptions, SamplingParams
 """

@@ -20,7 +20,7 @@ import sys
 
 
 def parse_args(argv=None):
-    ap = argparse.ArgumentParser(prog="vllm-oxide", description="Single-GPU (B200) Qwen3 inference engine")
+    ap = argparse.ArgumentParser(prog="vllm-oxide", description="Single-GPU (B200) inference engine (Qwen3 dense, Tofilorn)")
     ap.add_argument("-m", "--model", default=None, help="local model folder (config.json + safetensors)")
     ap.add_argument("--random-weights", action="store_true",
                     help="no model folder: seeded random weights for the model of --config")

@@ -104,15 +104,18 @@ mingru_scan_kernel(const T* zxg, const T* __restrict__ bz, const T* __restrict__
 // blocks as there are ranges.  MODE 0 is the walk from the slot's state to the slot's state in one launch.
 constexpr int HG_TT = 16;
 
-__device__ __forceinline__ int hg_pad(int i) { return i + (i >> 5); }
+// index of gate i in a row of shared memory: four floats of padding after every 32, so that the lanes that share a column
+// (32 or 64 rows apart) read different banks with 16-byte loads
+__device__ __forceinline__ int hg_pad(int i) { return i + 4 * (i >> 5); }
 
 template <typename T, int R, int PARTS, bool FUSE, int MODE>
 __global__ void __launch_bounds__(FUSE ? (R > 32 ? 256 : 512) : 128)
 hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restrict__ lower, const float* __restrict__ nw,
                   float* state, const int* __restrict__ cu_q, const int* __restrict__ state_slots, T* out, float* raw,
                   float* ends, float* gates, int heads, int dk, int dv, int col_blocks, float eps, int num_slots, int* err) {
-  extern __shared__ float sm[];
-  const int gate_row = hg_pad(R * PARTS) + 1;
+  extern __shared__ float4 sm4[];
+  float* sm = reinterpret_cast<float*>(sm4);
+  const int gate_row = hg_pad(R * PARTS);
   const int cols = blockDim.x / PARTS;
   float* qs = sm;                        // [HG_TT][gate_row]
   float* fs = qs + HG_TT * gate_row;     // [HG_TT][gate_row]
@@ -144,15 +147,32 @@ hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restric
     for (int i = 0; i < R; ++i) F[MODE == 1 ? i : 0] = 1.f;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  // the gates of a tile: thread rows over tokens, thread columns over gates (one division, here)
+  const int gate_lanes = min(dk, (int)blockDim.x), gate_step = blockDim.x / gate_lanes;
+  const int gate_i = threadIdx.x % gate_lanes, gate_t = threadIdx.x / gate_lanes < gate_step ? threadIdx.x / gate_lanes : HG_TT;
   for (int ts = t0; ts < t1; ts += HG_TT) {
     const int n = min(HG_TT, t1 - ts);
-    for (int idx = threadIdx.x; idx < n * dk; idx += blockDim.x) {
-      const int tt = idx / dk, i = idx % dk;
-      const T* row = qfv + (size_t)(ts + tt) * width;
-      const float qv = to_f<T>(row[h * dk + i]);
-      qs[tt * gate_row + hg_pad(i)] = qv * sigmoid_f(qv);
-      const float l = lower[h * dk + i];
-      fs[tt * gate_row + hg_pad(i)] = l + (1.f - l) * sigmoid_f(to_f<T>(row[(heads + h) * dk + i]) + to_f<T>(bf[h * dk + i]));
+    for (int i = gate_i; i < dk; i += gate_lanes) {
+      const float l = lower[h * dk + i], bias = to_f<T>(bf[h * dk + i]);
+      // eight tokens' loads are issued before the first of them is used
+      for (int tb = gate_t; tb < n; tb += 8 * gate_step) {
+        float qa[8], fa[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int tt = min(tb + k * gate_step, n - 1);
+          const T* row = qfv + (size_t)(ts + tt) * width;
+          qa[k] = to_f<T>(row[h * dk + i]);
+          fa[k] = to_f<T>(row[(heads + h) * dk + i]);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int tt = tb + k * gate_step;
+          if (tt < n) {
+            qs[tt * gate_row + hg_pad(i)] = qa[k] * sigmoid_f(qa[k]);
+            fs[tt * gate_row + hg_pad(i)] = l + (1.f - l) * sigmoid_f(fa[k] + bias);
+          }
+        }
+      }
     }
     for (int idx = threadIdx.x; idx < n * cols; idx += blockDim.x) {
       const int tt = idx / cols, c = idx % cols;
@@ -165,13 +185,18 @@ hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restric
       const float* fr = fs + tt * gate_row + hg_pad(i0);
       const float* qr = qs + tt * gate_row + hg_pad(i0);
 #pragma unroll
-      for (int i = 0; i < R; ++i)
-        if (i0 + i < dk) {
-          const float f = fr[i + (i >> 5)];      // hg_pad(i0 + i): i0 is a multiple of 32 wherever R exceeds it
-          M[i] = fmaf(f, M[i], (1.f - f) * v);
-          if (MODE == 1) F[MODE == 1 ? i : 0] *= f;
-          else o = fmaf(M[i], qr[i + (i >> 5)], o);
-        }
+      for (int i = 0; i < R; i += 4) {
+        const float4 f4 = *reinterpret_cast<const float4*>(fr + hg_pad(i));      // hg_pad(i0 + i) = hg_pad(i0) + hg_pad(i)
+        const float4 q4 = MODE == 1 ? f4 : *reinterpret_cast<const float4*>(qr + hg_pad(i));
+        const float fv[4] = {f4.x, f4.y, f4.z, f4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (i0 + i + k < dk) {
+            M[i + k] = fmaf(fv[k], M[i + k], (1.f - fv[k]) * v);
+            if (MODE == 1) F[MODE == 1 ? i + k : 0] *= fv[k];
+            else o = fmaf(M[i + k], qv[k], o);
+          }
+      }
       if (MODE != 1) {
 #pragma unroll
         for (int d = 1; d < PARTS; d <<= 1) o += __shfl_xor_sync(0xffffffffu, o, d);
@@ -246,7 +271,7 @@ template <typename T, int R, int PARTS, int MODE>
 int launch_hgrn2(const void* qfv, const void* bf, const float* lower, const float* nw, float* state, const int* cu_q,
                  const int* state_slots, void* out, float* raw, float* ends, float* gates, int B, int chunks, int heads, int dk,
                  int dv, float eps, int num_slots, int fuse, int* err, cudaStream_t stream) {
-  const int gate_row = R * PARTS + (R * PARTS) / 32 + 1;
+  const int gate_row = R * PARTS + 4 * ((R * PARTS) / 32);
   const int threads = fuse ? (dv * PARTS + 31) / 32 * 32 : 128;
   const int cols = threads / PARTS;
   const int col_blocks = fuse ? 1 : (dv + cols - 1) / cols;

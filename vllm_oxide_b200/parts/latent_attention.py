@@ -38,6 +38,21 @@ from .linear import linear
 
 
 FAST_GROUP = 16     # query heads that the tensor-core attention kernels take for one key head
+# bfloat16 steps of more than 16 tokens: the per-head products go to the library's batched product (as the package's other
+# products of that size do); smaller steps and the 32-bit path use head_linear
+LIBRARY_HEAD_PRODUCTS = True
+
+
+def head_product(x, x_width: int, x_used: int, w, y, y_width: int, T: int) -> None:
+    """y[t, h, :O] = x[t, h, :x_used] @ w[h] for w [heads, x_used, O]; x is [T, heads * x_width], y [T, heads * y_width]
+    (either may be columns of a wider buffer: their row strides are taken from the tensors)."""
+    heads, I, O = w.shape
+    if LIBRARY_HEAD_PRODUCTS and x.dtype == torch.bfloat16 and T > 16:
+        a = torch.as_strided(x, (heads, T, I), (x_width, x.stride(0), 1))
+        out = torch.as_strided(y, (heads, T, O), (y_width, y.stride(0), 1))
+        torch.bmm(a, w, out=out)
+    else:
+        kernels.head_linear(x, x.stride(0), x_width, w, y, y.stride(0), y_width, T)
 
 
 class LatentAttention(Mixer):
@@ -108,7 +123,7 @@ class LatentAttention(Mixer):
         q = linear(cq, self.wuq, ctx.ws.get("latent_q", T, nh * (self.dk + self.dr), x.dtype), ctx)
         # every query head into the latent's space, its rotated part behind: a query row is shaped like a cache row
         qa = ctx.ws.get("latent_qa", T, nh * self.row, x.dtype)
-        kernels.head_linear(q, nh * (self.dk + self.dr), self.dk + self.dr, self.wuk, qa, nh * self.row, self.row, T)
+        head_product(q, self.dk + self.dr, self.dk, self.wuk, qa, self.row, T)
         kernels.latent_query_rotate(q, qa, self.rotation, ctx.positions, T, nh, self.dk, self.dr, self.kv_rank, self.row)
         heads = ctx.ws.get("latent_heads", T, nh * self.dv, x.dtype)
         # the tensor-core kernels take up to FAST_GROUP query heads for one key head: more heads go in groups, each with
@@ -121,8 +136,9 @@ class LatentAttention(Mixer):
             w = paged_attend(qa[:, h0 * self.row:(h0 + n) * self.row], nh * self.row, mixed, cache.k, cache.k, cache.group, ctx, T,
                              n, 1, self.row, self.window, self.scale, self._pairs[k] if self._pairs else None,
                              value_dim=self.kv_rank)
-            kernels.head_linear(mixed, n * w, w, self.wuv[h0:h0 + n], heads[:, h0 * self.dv:(h0 + n) * self.dv], nh * self.dv,
-                                self.dv, T)
+            # the plain kernel packs rows of n * w elements into the buffer, the tensor-core kernels fill its rows
+            packed = mixed if w == self.row else mixed.reshape(-1)[:T * n * w].view(T, n * w)
+            head_product(packed, w, self.kv_rank, self.wuv[h0:h0 + n], heads[:, h0 * self.dv:(h0 + n) * self.dv], self.dv, T)
         return linear(heads, self.wo, ctx.ws.get("mixer_proj", T, self.H, x.dtype), ctx)
 
 
