@@ -96,37 +96,50 @@ __global__ void latent_query_rotate_kernel(const T* q, T* qa, const float* __res
   }
 }
 
-// y[t, h, o] = sum_i w[h][i][o] * x[t, h, i]; w is [heads, I, O] with O contiguous.  A block takes HL_TT tokens, one head and 128
-// outputs: the tokens' inputs wait in shared memory as floats and every weight is read once for all of them.  Each output is one
-// chain of multiply-adds over i in ascending order, whatever the tile it falls into.
-constexpr int HL_TT = 8, HL_NT = 128;
+// y[t, h, o] = sum_i w[h][i][o] * x[t, h, i]; w is [heads, I, O] with O contiguous.  A block takes HL_TT tokens, one head and 32
+// outputs; the tokens' inputs wait in shared memory as floats.  Warp k multiplies the inputs i = k, k + 8, ... (its loads of
+// w do not depend on one another, so many are in flight: with a few tokens the kernel is a chain of memory latencies, and
+// eight short chains side by side end eight times sooner than one); the eight partial sums of an output are then added in
+// the order of the warps.  The order of operations of an output depends on I alone, not on the tile it falls into.
+constexpr int HL_TT = 8, HL_WARPS = 8, HL_O = 32;
 
 template <typename T>
-__global__ void __launch_bounds__(HL_NT)
+__global__ void __launch_bounds__(HL_WARPS * 32)
 head_linear_kernel(const T* x, long x_ts, long x_hs, const T* __restrict__ w, T* y, long y_ts, long y_hs, int tokens, int I, int O) {
-  extern __shared__ float xs[];  // [HL_TT][I]
+  extern __shared__ float xs[];                 // [HL_TT][I], then the partial sums [HL_WARPS][HL_TT][HL_O]
+  float* part = xs + HL_TT * I;
   pdl_launch_dependents();
   pdl_wait();
-  const int h = blockIdx.y, t0 = blockIdx.z * HL_TT, o = blockIdx.x * HL_NT + threadIdx.x;
+  const int h = blockIdx.y, t0 = blockIdx.z * HL_TT, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int o = blockIdx.x * HL_O + lane;
   const int n = min(HL_TT, tokens - t0);
-  for (int idx = threadIdx.x; idx < HL_TT * I; idx += HL_NT) {
+  for (int idx = threadIdx.x; idx < HL_TT * I; idx += HL_WARPS * 32) {
     const int tt = idx / I, i = idx % I;
     xs[idx] = tt < n ? to_f<T>(x[(size_t)(t0 + tt) * x_ts + (size_t)h * x_hs + i]) : 0.f;
   }
   __syncthreads();
-  if (o >= O) return;
   float acc[HL_TT];
 #pragma unroll
   for (int tt = 0; tt < HL_TT; ++tt) acc[tt] = 0.f;
-  const T* wh = w + (size_t)h * I * O + o;
-  for (int i = 0; i < I; ++i) {
-    const float wv = to_f<T>(wh[(size_t)i * O]);
+  if (o < O) {
+    const T* wh = w + (size_t)h * I * O + o;
+#pragma unroll 8
+    for (int i = warp; i < I; i += HL_WARPS) {
+      const float wv = to_f<T>(wh[(size_t)i * O]);
 #pragma unroll
-    for (int tt = 0; tt < HL_TT; ++tt) acc[tt] = fmaf(wv, xs[tt * I + i], acc[tt]);
+      for (int tt = 0; tt < HL_TT; ++tt) acc[tt] = fmaf(wv, xs[tt * I + i], acc[tt]);
+    }
   }
 #pragma unroll
-  for (int tt = 0; tt < HL_TT; ++tt)
-    if (tt < n) y[(size_t)(t0 + tt) * y_ts + (size_t)h * y_hs + o] = from_f<T>(acc[tt]);
+  for (int tt = 0; tt < HL_TT; ++tt) part[(warp * HL_TT + tt) * HL_O + lane] = acc[tt];
+  __syncthreads();
+  const int tt = warp;                          // eight warps, eight tokens: warp k sums token k's partial sums
+  if (o < O && tt < n) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < HL_WARPS; ++k) s += part[(k * HL_TT + tt) * HL_O + lane];
+    y[(size_t)(t0 + tt) * y_ts + (size_t)h * y_hs + o] = from_f<T>(s);
+  }
 }
 
 }  // namespace vob
@@ -172,14 +185,14 @@ VOB_API int vob_head_linear(const void* x, long x_ts, long x_hs, const void* w, 
                             int I, int O, int dtype, cudaStream_t stream) {
   if (T <= 0 || heads <= 0 || O <= 0) return 0;
   if (I <= 0) return VOB_BAD_ARGUMENT;
-  const size_t smem = (size_t)HL_TT * I * sizeof(float);
-  dim3 grid((O + HL_NT - 1) / HL_NT, heads, (T + HL_TT - 1) / HL_TT);
+  const size_t smem = ((size_t)HL_TT * I + (size_t)HL_WARPS * HL_TT * HL_O) * sizeof(float);
+  dim3 grid((O + HL_O - 1) / HL_O, heads, (T + HL_TT - 1) / HL_TT);
   if (smem > 48 * 1024 || grid.y > 65535 || grid.z > 65535) return VOB_UNSUPPORTED;
   if (dtype == VOB_F32)
-    return launch_kernel(head_linear_kernel<float>, grid, dim3(HL_NT), smem, stream, (const float*)x, x_ts, x_hs, (const float*)w,
+    return launch_kernel(head_linear_kernel<float>, grid, dim3(HL_WARPS * 32), smem, stream, (const float*)x, x_ts, x_hs, (const float*)w,
                          (float*)y, y_ts, y_hs, T, I, O);
   if (dtype == VOB_BF16)
-    return launch_kernel(head_linear_kernel<__nv_bfloat16>, grid, dim3(HL_NT), smem, stream, (const __nv_bfloat16*)x, x_ts, x_hs,
+    return launch_kernel(head_linear_kernel<__nv_bfloat16>, grid, dim3(HL_WARPS * 32), smem, stream, (const __nv_bfloat16*)x, x_ts, x_hs,
                          (const __nv_bfloat16*)w, (__nv_bfloat16*)y, y_ts, y_hs, T, I, O);
   return VOB_BAD_ARGUMENT;
 }
