@@ -359,9 +359,12 @@ def tofilorn_kernel_bytes(cfg: dict, T: int) -> dict:
     for l in cfg["layers"]:
         m = l["mixer"]
         subs = 2 if l["mlp"] else 1
+        if l["mlp"]:
+            b["silu_mul"] = b.get("silu_mul", 0) + T * 3 * l["mlp"]["ff"] * 2
         b["stream_step"] += subs * T * (2 * S * D * 4 + 2 * D * 2)                # streams read and written, y in, normed out
         if l["type"] == "mingru":
             b["mingru_scan"] += T * 4 * m["width"] * 2
+            b["silu_mul"] = b.get("silu_mul", 0)
         elif l["type"] == "hgrn2":
             b["hgrn2_scan"] += T * m["heads"] * (2 * m["dim"] + 2 * m["vdim"]) * 2
         else:
@@ -370,6 +373,15 @@ def tofilorn_kernel_bytes(cfg: dict, T: int) -> dict:
             b["latent_query_rotate"] += T * m["heads"] * 2 * m["rot_dim"] * 2
             b["head_linear"] += (T * m["heads"] * (m["dim"] + 2 * row + m["vdim"]) + 2 * m["heads"] * m["kv_rank"] * (m["dim"] + m["vdim"])) * 2
     return b
+
+
+def qwen3_kernel_bytes(cfg: dict, T: int) -> dict:
+    """The same for the row-wise kernels of a Qwen3 step: add+norm reads the stream and writes the normed rows (the sum was made
+    by the product before), the q/k kernel reads q|k|v, writes q and k back and k, v to the cache, SiLU*up reads 2I and writes I."""
+    L, D, I = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"]
+    nh, kvh, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    return {"add_rmsnorm": 2 * L * T * D * 2 * 2, "silu_mul": L * T * 3 * I * 2,
+            "qk_norm_rope_kv_write": L * T * ((nh + 2 * kvh) + (nh + kvh) + 2 * kvh) * hd * 2}
 
 
 def tofilorn_run(widths, pk=None, layers: int = 16) -> dict:
@@ -407,9 +419,9 @@ def tofilorn_run(widths, pk=None, layers: int = 16) -> dict:
                     kernels.enable_kernel_timers(False)
                 del llm
                 torch.cuda.empty_cache()
-            if name == "tofilorn":
+            if True:
                 for key, T in (("prefill_2048", PROMPT_LEN), ("decode_batch8", 8)):
-                    ms, by = r[key]["own_kernels_ms"], tofilorn_kernel_bytes(cfg, T)
+                    ms, by = r[key]["own_kernels_ms"], (tofilorn_kernel_bytes if name == "tofilorn" else qwen3_kernel_bytes)(cfg, T)
                     r[key]["own_kernels_frac_of_copy"] = {k: round(by[k] / (ms[k] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
                                                           for k in by if ms.get(k)}
             rec[name] = r

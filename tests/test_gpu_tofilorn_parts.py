@@ -247,7 +247,8 @@ def plain_latent(spec, x, kept=None):
 
 
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("case", ["odd sizes", "a window of one page, cache row of 64", "no window, wide latent", "rotated part wider than rotated dims"])
+@pytest.mark.parametrize("case", ["odd sizes", "a window of one page, cache row of 64", "no window, wide latent", "rotated part wider than rotated dims",
+                                  "more heads than the tensor-core kernels take at once"])
 def test_latent_attention_alone_with_one_loud_key(case, dt):
     """One token's shared key part is made 60 times larger than the others: for about half of the (query, head) pairs its
     score then drowns all others, so a query that sees it by mistake, or misses it, gives another row altogether."""
@@ -262,6 +263,9 @@ def test_latent_attention_alone_with_one_loud_key(case, dt):
     elif case == "no window, wide latent":
         H, W = 64, 0
         specs = latent_parts(dt, H, 2, 64, 32, 64, 128, 96, 0.1, dict(dims=32, base=500.0, scaling=dict(factor=8.0, original=64, fast=4.0, slow=2.0)), None)
+    elif case == "more heads than the tensor-core kernels take at once":
+        H, W = 64, 40         # 21 heads: a group of 16 and a group of 5 in bfloat16, all at once in 32-bit
+        specs = latent_parts(dt, H, 21, 16, 8, 16, 32, 24, 0.25, dict(dims=8, base=300.0), W)
     else:
         H, W = 32, 7
         specs = latent_parts(dt, H, 1, 32, 16, 16, 16, 24, 0.2, dict(dims=8, base=100.0), W)

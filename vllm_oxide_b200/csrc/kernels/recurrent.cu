@@ -9,6 +9,8 @@
 namespace vob {
 
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+// f = l + (1 - l) sigmoid(pre + bias): one spelling for every kernel that needs the gate
+__device__ __forceinline__ float forget_gate(float l, float pre, float bias) { return fmaf(1.f - l, sigmoid_f(pre + bias), l); }
 
 // ---------------------------------------------------------------- minGRU
 // zxg [tokens, 3W]: pre-activations of the gate z, of the candidate u and of the output gate g (no bias yet).
@@ -97,8 +99,9 @@ mingru_scan_kernel(const T* zxg, const T* __restrict__ bz, const T* __restrict__
 // over more blocks, o leaves in float and head_gain_norm_kernel follows.  Both give the same numbers: an element's
 // chain of operations depends on (R, PARTS) alone, and those follow from dk.
 //
-// A long portion is also cut along the tokens (`chunks` > 1, three launches): MODE 1 walks every range from a zero state
-// and leaves its end state L and the product F of its gates; hgrn2_join_kernel goes through the ranges in order,
+// A long portion is also cut along the tokens (`chunks` > 1, four launches): MODE 1 walks every range from a zero state
+// and leaves its end state L; hgrn2_range_gates_kernel takes the product F of every range's gates; hgrn2_join_kernel goes
+// through the ranges in order,
 // M_start(c+1) = diag(F_c) M_start(c) + L_c, leaves every range's start where its L was and the last state in the
 // slot; MODE 2 walks the ranges again from their starts and writes the outputs.  Twice the arithmetic, on as many more
 // blocks as there are ranges.  MODE 0 is the walk from the slot's state to the slot's state in one launch.
@@ -108,7 +111,8 @@ constexpr int HG_TT = 16;
 // (32 or 64 rows apart) read different banks with 16-byte loads
 __device__ __forceinline__ int hg_pad(int i) { return i + 4 * (i >> 5); }
 
-template <typename T, int R, int PARTS, bool FUSE, int MODE>
+// FULL: dk = R * PARTS, every row a thread holds exists (no test per element: the tests were two of seven instructions).
+template <typename T, int R, int PARTS, bool FUSE, int MODE, bool FULL>
 __global__ void __launch_bounds__(FUSE ? (R > 32 ? 256 : 512) : 128)
 hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restrict__ lower, const float* __restrict__ nw,
                   float* state, const int* __restrict__ cu_q, const int* __restrict__ state_slots, T* out, float* raw,
@@ -118,8 +122,9 @@ hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restric
   const int gate_row = hg_pad(R * PARTS);
   const int cols = blockDim.x / PARTS;
   float* qs = sm;                        // [HG_TT][gate_row]
-  float* fs = qs + HG_TT * gate_row;     // [HG_TT][gate_row]
-  float* vs = fs + HG_TT * gate_row;     // [HG_TT][cols]
+  float* fs = qs + HG_TT * gate_row;     // [HG_TT][gate_row]  f
+  float* gs = fs + HG_TT * gate_row;     // [HG_TT][gate_row]  1 - f
+  float* vs = gs + HG_TT * gate_row;     // [HG_TT][cols]
   float* os = vs + HG_TT * cols;         // [HG_TT][cols]  (FUSE)
   pdl_launch_dependents();
   const int part = threadIdx.x % PARTS, jj = threadIdx.x / PARTS;
@@ -139,13 +144,9 @@ hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restric
   const int i0 = part * R;
   float* mine = MODE == 0 ? state + (((size_t)slot * heads + h) * dk + i0) * dv + j
                           : ends + ((((size_t)b * chunks + chunk) * heads + h) * dk + i0) * dv + j;
-  float M[R], F[MODE == 1 ? R : 1];
+  float M[R];
 #pragma unroll
   for (int i = 0; i < R; ++i) M[i] = (MODE != 1 && i0 + i < dk && j < dv) ? mine[(size_t)i * dv] : 0.f;
-  if (MODE == 1) {
-#pragma unroll
-    for (int i = 0; i < R; ++i) F[MODE == 1 ? i : 0] = 1.f;
-  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   // the gates of a tile: thread rows over tokens, thread columns over gates (one division, here)
   const int gate_lanes = min(dk, (int)blockDim.x), gate_step = blockDim.x / gate_lanes;
@@ -168,8 +169,10 @@ hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restric
         for (int k = 0; k < 8; ++k) {
           const int tt = tb + k * gate_step;
           if (tt < n) {
-            qs[tt * gate_row + hg_pad(i)] = qa[k] * sigmoid_f(qa[k]);
-            fs[tt * gate_row + hg_pad(i)] = l + (1.f - l) * sigmoid_f(fa[k] + bias);
+            const float f = forget_gate(l, fa[k], bias);
+            if (MODE != 1) qs[tt * gate_row + hg_pad(i)] = qa[k] * sigmoid_f(qa[k]);
+            fs[tt * gate_row + hg_pad(i)] = f;
+            gs[tt * gate_row + hg_pad(i)] = 1.f - f;
           }
         }
       }
@@ -183,18 +186,19 @@ hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restric
       float o = 0.f;
       const float v = vs[tt * cols + jj];
       const float* fr = fs + tt * gate_row + hg_pad(i0);
+      const float* gr = gs + tt * gate_row + hg_pad(i0);
       const float* qr = qs + tt * gate_row + hg_pad(i0);
 #pragma unroll
       for (int i = 0; i < R; i += 4) {
         const float4 f4 = *reinterpret_cast<const float4*>(fr + hg_pad(i));      // hg_pad(i0 + i) = hg_pad(i0) + hg_pad(i)
+        const float4 g4 = *reinterpret_cast<const float4*>(gr + hg_pad(i));
         const float4 q4 = MODE == 1 ? f4 : *reinterpret_cast<const float4*>(qr + hg_pad(i));
-        const float fv[4] = {f4.x, f4.y, f4.z, f4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w};
+        const float fv[4] = {f4.x, f4.y, f4.z, f4.w}, gv[4] = {g4.x, g4.y, g4.z, g4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          if (i0 + i + k < dk) {
-            M[i + k] = fmaf(fv[k], M[i + k], (1.f - fv[k]) * v);
-            if (MODE == 1) F[MODE == 1 ? i + k : 0] *= fv[k];
-            else o = fmaf(M[i + k], qv[k], o);
+          if (FULL || i0 + i + k < dk) {
+            M[i + k] = fmaf(fv[k], M[i + k], gv[k] * v);
+            if (MODE != 1) o = fmaf(M[i + k], qv[k], o);
           }
       }
       if (MODE != 1) {
@@ -225,16 +229,45 @@ hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restric
     for (int i = 0; i < R; ++i)
       if (i0 + i < dk) mine[(size_t)i * dv] = M[i];
   }
-  if (MODE == 1 && j == 0) {
-    float* g = gates + (((size_t)b * chunks + chunk) * heads + h) * dk + i0;
+}
+
+// gates[b][c][h][i] = the product of the forget gates of range c of request b: what an end state of that range owes to its start.
+// A block takes 32 gates of one range; its eight warps take every eighth token, and their partial products are multiplied
+// in the order of the warps.
+template <typename T>
+__global__ void __launch_bounds__(256)
+hgrn2_range_gates_kernel(const T* qfv, const T* __restrict__ bf, const float* __restrict__ lower, float* gates,
+                         const int* __restrict__ cu_q, int heads, int dk, int dv) {
+  __shared__ float part[8][32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.y, chunk = blockIdx.z, chunks = gridDim.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = min(blockIdx.x * 32 + lane, heads * dk - 1);      // (head, i)
+  const int q0 = cu_q[b], q1 = cu_q[b + 1];
+  if (q1 <= q0) return;
+  const int per = (q1 - q0 + chunks - 1) / chunks;
+  const int t0 = min(q1, q0 + chunk * per), t1 = min(q1, t0 + per);
+  const size_t width = (size_t)heads * (2 * dk + dv);
+  const float l = lower[e], bias = to_f<T>(bf[e]);
+  float F = 1.f;
+#pragma unroll 4
+  for (int t = t0 + warp; t < t1; t += 8) F *= forget_gate(l, to_f<T>(qfv[(size_t)t * width + (size_t)heads * dk + e]), bias);
+  part[warp][lane] = F;
+  __syncthreads();
+  if (warp == 0 && blockIdx.x * 32 + lane < heads * dk) {
+    F = part[0][lane];
 #pragma unroll
-    for (int i = 0; i < R; ++i)
-      if (i0 + i < dk) g[i] = F[MODE == 1 ? i : 0];
+    for (int k = 1; k < 8; ++k) F *= part[k][lane];
+    gates[((size_t)b * chunks + chunk) * heads * dk + e] = F;
   }
 }
 
-// One thread per element of a request's state: through the ranges in order, start(c) takes the place of L_c.
-__global__ void hgrn2_join_kernel(float* state, float* ends, const float* gates, const int* __restrict__ cu_q,
+// One thread per element of a request's state: through the ranges in order, start(c) takes the place of L_c.  All of a
+// thread's loads are issued before its first store (at most HG_MAX_CHUNKS ranges), or every store would wait for a load.
+constexpr int HG_MAX_CHUNKS = 16;
+
+__global__ void hgrn2_join_kernel(float* state, float* ends, const float* __restrict__ gates, const int* __restrict__ cu_q,
                                   const int* __restrict__ state_slots, int chunks, int heads, int dk, int dv, int num_slots) {
   pdl_launch_dependents();
   pdl_wait();
@@ -243,13 +276,20 @@ __global__ void hgrn2_join_kernel(float* state, float* ends, const float* gates,
   const int slot = state_slots[b];
   if (e >= per || cu_q[b + 1] <= cu_q[b] || slot < 0 || slot >= num_slots) return;
   const long row = e / dv;      // (head, i)
+  float L[HG_MAX_CHUNKS], F[HG_MAX_CHUNKS];
+#pragma unroll
+  for (int c = 0; c < HG_MAX_CHUNKS; ++c)
+    if (c < chunks) {
+      L[c] = ends[((size_t)b * chunks + c) * per + e];
+      F[c] = gates[((size_t)b * chunks + c) * heads * dk + row];
+    }
   float M = state[(size_t)slot * per + e];
-  for (int c = 0; c < chunks; ++c) {
-    float* L = ends + ((size_t)b * chunks + c) * per + e;
-    const float l = *L, f = gates[((size_t)b * chunks + c) * heads * dk + row];
-    *L = M;
-    M = fmaf(f, M, l);
-  }
+#pragma unroll
+  for (int c = 0; c < HG_MAX_CHUNKS; ++c)
+    if (c < chunks) {
+      ends[((size_t)b * chunks + c) * per + e] = M;
+      M = fmaf(F[c], M, L[c]);
+    }
   state[(size_t)slot * per + e] = M;
 }
 
@@ -275,13 +315,18 @@ int launch_hgrn2(const void* qfv, const void* bf, const float* lower, const floa
   const int threads = fuse ? (dv * PARTS + 31) / 32 * 32 : 128;
   const int cols = threads / PARTS;
   const int col_blocks = fuse ? 1 : (dv + cols - 1) / cols;
-  const size_t smem = ((size_t)2 * HG_TT * gate_row + (fuse ? 2 : 1) * (size_t)HG_TT * cols) * sizeof(float);
+  const size_t smem = ((size_t)3 * HG_TT * gate_row + (fuse ? 2 : 1) * (size_t)HG_TT * cols) * sizeof(float);
   dim3 grid(heads * col_blocks, B, chunks);
   if (fuse)
-    return launch_kernel(hgrn2_scan_kernel<T, R, PARTS, true, 0>, grid, dim3(threads), smem, stream, (const T*)qfv, (const T*)bf,
+    return launch_kernel(hgrn2_scan_kernel<T, R, PARTS, true, 0, false>, grid, dim3(threads), smem, stream, (const T*)qfv, (const T*)bf,
                          lower, nw, state, cu_q, state_slots, (T*)out, raw, ends, gates, heads, dk, dv, col_blocks, eps, num_slots, err);
-  return launch_kernel(hgrn2_scan_kernel<T, R, PARTS, false, MODE>, grid, dim3(threads), smem, stream, (const T*)qfv, (const T*)bf,
-                       lower, nw, state, cu_q, state_slots, (T*)out, raw, ends, gates, heads, dk, dv, col_blocks, eps, num_slots, err);
+  if (dk == R * PARTS)
+    return launch_kernel(hgrn2_scan_kernel<T, R, PARTS, false, MODE, true>, grid, dim3(threads), smem, stream, (const T*)qfv,
+                         (const T*)bf, lower, nw, state, cu_q, state_slots, (T*)out, raw, ends, gates, heads, dk, dv, col_blocks, eps,
+                         num_slots, err);
+  return launch_kernel(hgrn2_scan_kernel<T, R, PARTS, false, MODE, false>, grid, dim3(threads), smem, stream, (const T*)qfv,
+                       (const T*)bf, lower, nw, state, cu_q, state_slots, (T*)out, raw, ends, gates, heads, dk, dv, col_blocks, eps,
+                       num_slots, err);
 }
 
 // rows of the state a thread keeps, and lanes that share a column: from dk alone
@@ -313,6 +358,9 @@ int dispatch_hgrn2(const void* qfv, const void* bf, const float* lower, const fl
     float* gates = scratch + (size_t)B * chunks * heads * dk * dv;
     code = dispatch_hgrn2_mode<T, 1>(qfv, bf, lower, nw, state, cu_q, state_slots, out, raw, ends, gates, B, chunks, heads, dk, dv,
                                      eps, num_slots, 0, err, stream);
+    if (code != 0) return code;
+    code = launch_kernel(hgrn2_range_gates_kernel<T>, dim3((heads * dk + 31) / 32, B, chunks), dim3(256), 0, stream, (const T*)qfv,
+                         (const T*)bf, lower, gates, cu_q, heads, dk, dv);
     if (code != 0) return code;
     const long per = (long)heads * dk * dv;
     code = launch_kernel(hgrn2_join_kernel, dim3((unsigned)((per + 255) / 256), B), dim3(256), 0, stream, state, ends,
@@ -368,7 +416,7 @@ VOB_API int vob_hgrn2_scan(const void* qfv, const void* bf, const float* lower, 
                            int dk, int dv, float eps, int num_slots, int fuse, int dtype, int* err, cudaStream_t stream) {
   if (B <= 0 || T <= 0) return 0;
   if (heads <= 0 || dk <= 0 || dv <= 0 || dk > 256 || B > 65535 || (!fuse && !raw) || (fuse && !vob_hgrn2_can_fuse(dk, dv)) ||
-      chunks < 1 || chunks > 64 || (chunks > 1 && (fuse || !scratch)))
+      chunks < 1 || chunks > HG_MAX_CHUNKS || (chunks > 1 && (fuse || !scratch)))
     return VOB_UNSUPPORTED;
   if (dtype == VOB_F32)
     return dispatch_hgrn2<float>(qfv, bf, lower, nw, state, cu_q, state_slots, out, raw, scratch, T, B, chunks, heads, dk, dv, eps,

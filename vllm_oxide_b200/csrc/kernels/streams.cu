@@ -94,6 +94,129 @@ stream_step_kernel(float* streams, const T* y, const T* init, const float* __res
   for (int d = threadIdx.x; d < D; d += STREAM_NT) normed[(size_t)r * D + d] = from_f<T>(urow[d] / denom * g);
 }
 
+// The same with 16-byte accesses: a thread takes four neighbouring elements of every stream (D a multiple of 4, rows that
+// start on 16-byte boundaries).  Which of the two kernels runs depends on D and S alone.
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 r = *reinterpret_cast<const float4*>(p);
+  v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, const float (&v)[4]);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+  uint2 r;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+  h[0] = __floats2bfloat162_rn(v[0], v[1]);
+  h[1] = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = r;
+}
+
+template <typename T, int MAXS>
+__global__ void __launch_bounds__(STREAM_NT)
+stream_step_vec_kernel(float* streams, const T* y, const T* init, const float* __restrict__ mix, const float* __restrict__ out_w,
+                       const float* __restrict__ in_w, const float* __restrict__ gain, T* normed, const int* __restrict__ rows,
+                       int num_src_rows, int S, int D, float eps, int* err) {
+  extern __shared__ float4 urow4[];  // D floats: the combined row (only with `normed`)
+  float* urow = reinterpret_cast<float*>(urow4);
+  __shared__ float scratch[32];
+  __shared__ float cm[MAXS * MAXS], co[MAXS], ci[MAXS];
+  pdl_launch_dependents();
+  for (int i = threadIdx.x; i < S * S; i += STREAM_NT) cm[i] = mix ? mix[i] : ((i / S == i % S) ? 1.f : 0.f);
+  for (int i = threadIdx.x; i < S; i += STREAM_NT) {
+    co[i] = out_w ? out_w[i] : 1.f;
+    ci[i] = in_w ? in_w[i] : 1.f;
+  }
+  const float g = gain ? gain[0] : 1.f;
+  pdl_wait();
+  const int r = blockIdx.x;
+  int src = r;
+  if (rows) {
+    src = rows[r];
+    if (src < 0 || src >= num_src_rows) {
+      if (threadIdx.x == 0) atomicOr(err, VOB_ERR_ROW);
+      return;
+    }
+  }
+  __syncthreads();
+  float* xs = streams + (size_t)src * S * D;
+  const bool store = rows == nullptr;
+  float ss = 0.f;
+  for (int d = threadIdx.x * 4; d < D; d += STREAM_NT * 4) {
+    float x[MAXS][4];
+    if (init) {
+      float e[4];
+      load4<T>(init + (size_t)src * D + d, e);
+#pragma unroll
+      for (int s = 0; s < MAXS; ++s)
+        if (s < S) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) x[s][k] = e[k];
+          if (store) store4<float>(xs + (size_t)s * D + d, e);
+        }
+    } else {
+#pragma unroll
+      for (int s = 0; s < MAXS; ++s) {
+        if (s < S) load4<float>(xs + (size_t)s * D + d, x[s]);
+        else x[s][0] = x[s][1] = x[s][2] = x[s][3] = 0.f;
+      }
+      if (y) {
+        float yv[4], nx[MAXS][4];
+        load4<T>(y + (size_t)src * D + d, yv);
+#pragma unroll
+        for (int t = 0; t < MAXS; ++t) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float a = 0.f;
+            if (t < S) {
+#pragma unroll
+              for (int s = 0; s < MAXS; ++s)
+                if (s < S) a = fmaf(cm[s * S + t], x[s][k], a);
+              a = fmaf(co[t], yv[k], a);
+            }
+            nx[t][k] = a;
+          }
+          if (t < S && store) store4<float>(xs + (size_t)t * D + d, nx[t]);
+        }
+#pragma unroll
+        for (int s = 0; s < MAXS; ++s)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) x[s][k] = nx[s][k];
+      }
+    }
+    if (normed) {
+      float u[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float a = 0.f;
+#pragma unroll
+        for (int s = 0; s < MAXS; ++s)
+          if (s < S) a = fmaf(ci[s], x[s][k], a);
+        u[k] = a;
+        ss += a * a;
+      }
+      store4<float>(urow + d, u);
+    }
+  }
+  if (!normed) return;
+  const float total = block_sum<STREAM_NT>(ss, scratch);
+  const float denom = sqrtf(total / (float)D + eps);
+  for (int d = threadIdx.x * 4; d < D; d += STREAM_NT * 4) {
+    float u[4];
+    load4<float>(urow + d, u);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) u[k] = u[k] / denom * g;
+    store4<T>(normed + (size_t)r * D + d, u);
+  }
+}
+
 // sums[t] = sum_s x_s (float [T, D]): what a single-stream model would call its residual stream.
 template <int MAXS>
 __global__ void stream_sum_kernel(const float* streams, float* sums, int S, int D) {
@@ -110,7 +233,9 @@ int launch_stream_step(float* streams, const void* y, const void* init, const fl
                        const float* gain, void* normed, const int* rows, int n_out, int n_src, int S, int D, float eps, int* err,
                        cudaStream_t stream) {
   const size_t smem = normed ? (size_t)D * sizeof(float) : 0;
-  auto k = stream_step_kernel<T, MAXS>;
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = MAXS <= 8 && D % 4 == 0 && aligned(streams) && aligned(y) && aligned(init) && aligned(normed);
+  auto k = vec ? stream_step_vec_kernel<T, (MAXS <= 8 ? MAXS : 1)> : stream_step_kernel<T, MAXS>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
