@@ -424,6 +424,22 @@ def tofilorn_run(widths, pk=None, layers: int = 16) -> dict:
                     ms, by = r[key]["own_kernels_ms"], (tofilorn_kernel_bytes if name == "tofilorn" else qwen3_kernel_bytes)(cfg, T)
                     r[key]["own_kernels_frac_of_copy"] = {k: round(by[k] / (ms[k] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
                                                           for k in by if ms.get(k)}
+                if name == "tofilorn" and r["prefill_2048"]["own_kernels_ms"].get("hgrn2_scan"):
+                    # the matrix-state scan is arithmetic, not traffic: float instructions a lane must issue (two walks of a
+                    # cut portion: multiply + multiply-add, then multiply + two multiply-adds, per state element and token)
+                    # against the device's float issue rate (SMs x 128 lanes x clock)
+                    prop = torch.cuda.get_device_properties(0)
+                    try:
+                        mhz = float(subprocess.run(["nvidia-smi", "--query-gpu=clocks.max.sm", "--format=csv,noheader,nounits", "-i", "0"],
+                                                   capture_output=True, text=True, timeout=20).stdout.split()[0])
+                    except (OSError, ValueError, IndexError, subprocess.SubprocessError):
+                        mhz = 0.0
+                    rate = prop.multi_processor_count * 128 * mhz * 1e6
+                    work = sum(PROMPT_LEN * l["mixer"]["heads"] * l["mixer"]["dim"] * l["mixer"]["vdim"] * 5
+                               for l in cfg["layers"] if l["type"] == "hgrn2")
+                    if rate:
+                        r["prefill_2048"]["hgrn2_scan_frac_of_float_issue_rate"] = round(
+                            work / (r["prefill_2048"]["own_kernels_ms"]["hgrn2_scan"] * 1e-3) / rate, 4)
             rec[name] = r
         out["sizes"][str(width)] = rec
     out["value"] = out["sizes"][str(widths[0])]["tofilorn"]["decode_batch8"]["tokens_per_s"]

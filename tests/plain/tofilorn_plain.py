@@ -160,7 +160,7 @@ def gated_ff(h, W, p):
 # ---------------------------------------------------------------- residual streams
 def stream_sublayer(X, W, hc, gain, eps, fn):
     """X [S, n, D].  u = sum_s a_s X_s; y = fn(norm(u)); X'_t = sum_s B[s, t] X_s + b_t y  (a = hc.in, b = hc.out,
-    B = hc.mix indexed [from, to]); all new streams are made from the old ones."""
+    B = hc.mix indexed [from, to]); the right-hand side uses the streams as they were before the sublayer."""
     u = torch.einsum("s,snd->nd", W[hc + "in"], X)
     y = fn(gain_norm(u, gain, eps))
     return torch.einsum("st,snd->tnd", W[hc + "mix"], X) + W[hc + "out"][:, None, None] * y[None]

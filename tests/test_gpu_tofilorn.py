@@ -278,3 +278,13 @@ def test_the_replay_program(folders, tmp_path):
         close(np.fromfile(out / "0.f32", "<f4").reshape(2, -1), want[[0, 29]], dtype, "step 0")
         close(np.fromfile(out / "1.f32", "<f4").reshape(1, -1), truth(folders, name, other, dtype)[[20]], dtype, "step 1")
         close(np.fromfile(out / "2.f32", "<f4").reshape(1, -1), want[[49]], dtype, "step 2")
+
+
+def test_the_command_line(folders):
+    name = "R"
+    prompt = tokens_for(name, 9, salt=900)
+    p = subprocess.run([os.path.join(ROOT, "bin", "vllm-oxide"), "-m", folders[name], "--token-ids", " ".join(map(str, prompt)),
+                        "--max-tokens", "6", "--dtype", "float32", "--ignore-eos", "--max-model-len", "128", "--block-size", "32",
+                        "--num-kv-blocks", "16"], capture_output=True, text=True, timeout=1200)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [int(t) for t in p.stdout.split()] == plain_greedy(folders, name, prompt, 6)

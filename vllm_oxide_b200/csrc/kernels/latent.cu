@@ -2,7 +2,7 @@
 // low-rank row per token.
 //
 //   latent_prep:   the down-projected row of a token is split into the query latent, the key/value latent and a rotated
-//                  key part shared by all heads; both latents are normalised (vector weights), the shared part is
+//                  key part that every head uses; both latents are normalised (vector weights), the shared part is
 //                  rotated by the token's position, and [latent | rotated part | zeros] is written to the token's slot
 //                  of the cache plane.  A layer that borrows another layer's plane only gets its query latent.
 //   head_linear:   y[t, h, :] = W_h x[t, h, :] for per-head matrices W_h: queries carried into the latent's space (so

@@ -3,7 +3,7 @@
 //
 // A token has S streams x_1..x_S of D floats, stored [token][stream][D].  One launch does, for every token,
 //   (1) either the start:   x_s = e  for all s (e: the embedded token), or, with y the output of the sublayer before,
-//       the update:         x'_t = sum_s M[s][t] x_s + b[t] * y      (all new streams from the old ones; M is [from][to])
+//       the update:         x'_t = sum_s M[s][t] x_s + b[t] * y      (the sum runs over the streams as they were; M is [from][to])
 //   (2) and, if asked:      u = sum_s a[s] x'_s ;  out = u / sqrt(mean(u^2) + eps) * g      (g: one number)
 // so that a sublayer costs one pass over the streams: S*D floats read and written, where the fused add+norm of a
 // single bfloat16 stream moves a quarter of that.  With one stream and M = a = b = 1 this is the plain residual sum in

@@ -8,7 +8,7 @@ With H heads, per head `dim` plain and `rot_dim` rotated query/key dimensions, v
     k_h = [W_uk,h c | r],  v_h = W_uv,h c;     score = (q_plain . k_plain + q_rot . r) * scale, window, softmax
     out = W_o [heads side by side]
 
-Only [c | r] is cached: one row of kv_rank + rot_dim elements a token, in a plane of one tensor and one "head", padded
+The cache holds [c | r] and nothing else: one row of kv_rank + rot_dim elements a token, in a plane of one tensor and one "head", padded
 with zeros to a multiple of 16 elements (the paged kernels read rows in 16-byte pieces).  Keys and values are never
 expanded.  Because k_plain = W_uk c, the plain part of a score is (W_uk,h^T q_plain) . c: every query head is carried
 into the latent's space once (`head_linear`), after which attention is multi-query attention whose key row is the cache

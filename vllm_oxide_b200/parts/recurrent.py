@@ -4,11 +4,11 @@ Both keep their state in float in the cache manager's state slots (`state_spec()
 a request's slot is zeroed when it is assigned.  Projections are the package's usual products (merged where several
 read the same input); gates, decays and the recurrence itself are float inside one scan kernel a mixer.
 
-`MinGRU`: gates that read only the current token.  z = sigmoid(Wz h + bz), u = Wx h + bx, candidate = u + 1/2 where
+`MinGRU`: both gates are functions of the current token alone, never of the state.  z = sigmoid(Wz h + bz), u = Wx h + bx, candidate = u + 1/2 where
 u >= 0 and sigmoid(u) below, s_t = (1 - z) s_{t-1} + z * candidate (element by element, `width` channels), output
 Wo (s_t * silu(Wg h)).  (The recurrence of Feng, Tung, Ahmed, Bengio and Hajimirsadeghi, "Were RNNs All We Needed?".)
 
-`HGRN2`: linear attention in which the forget gate also decides what is written.  Per head q = silu(Wq h) [dim],
+`HGRN2`: a matrix-valued state per head with one gate for two jobs: f keeps, 1 - f writes.  Per head q = silu(Wq h) [dim],
 v = Wv h [vdim], f = l + (1 - l) sigmoid(Wf h + bf) [dim] with a learned lower bound l; the state M [dim, vdim] goes
 M_t = diag(f_t) M_{t-1} + (1 - f_t) v_t^T, o_t = M_t^T q_t; o is RMS-normed over vdim (a weight shared by the heads),
 heads are concatenated and projected by Wo.

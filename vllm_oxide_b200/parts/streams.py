@@ -1,6 +1,6 @@
 """Several residual streams a token ("hyper-connections"), and the norm with a single gain that goes with them.
 
-Instead of one residual x a token carries S streams x_1..x_S, all equal to the embedded token at the start.  A sublayer
+A token carries S residual streams x_1..x_S instead of one; each begins as a copy of the embedded token.  A sublayer
 (the mixer, or the feed-forward) reads one combination of them and writes into all of them:
 
     u = sum_s a_s x_s;   y = sublayer(norm(u));   x'_t = sum_s B[s][t] x_s + b_t y      (B indexed [from][to])
