@@ -90,7 +90,7 @@ def in_portions(alone, rid, x, cuts, which=0):
 
 # ---------------------------------------------------------------- residual streams
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("S,D", [(1, 64), (3, 50), (4, 256), (5, 33), (16, 96)])
+@pytest.mark.parametrize("S,D", [(1, 64), (3, 50), (4, 256), (5, 33), (6, 64), (8, 128), (16, 96)])
 def test_stream_step(S, D, dt):
     from vllm_oxide_b200 import kernels
     n, eps = 7, 1e-5
@@ -180,7 +180,7 @@ def test_mingru_alone(H, W, dt):
 
 # ---------------------------------------------------------------- HGRN2
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("H,nh,dk,dv", [(48, 3, 16, 24), (64, 1, 64, 160), (32, 2, 128, 32), (40, 2, 20, 8)])
+@pytest.mark.parametrize("H,nh,dk,dv", [(48, 3, 16, 24), (64, 1, 64, 160), (32, 2, 128, 32), (40, 2, 20, 8), (32, 1, 256, 16), (32, 2, 200, 40)])
 def test_hgrn2_alone(H, nh, dk, dv, dt):
     from vllm_oxide_b200.parts import PartSpec, build_part
     eps = 1e-5

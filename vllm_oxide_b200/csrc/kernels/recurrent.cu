@@ -182,6 +182,7 @@ hgrn2_scan_kernel(const T* qfv, const T* __restrict__ bf, const float* __restric
       vs[idx] = cb * cols + c < dv ? to_f<T>(qfv[(size_t)(ts + tt) * width + (size_t)2 * heads * dk + h * dv + cb * cols + c]) : 0.f;
     }
     __syncthreads();
+#pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
       float o = 0.f;
       const float v = vs[tt * cols + jj];
@@ -317,16 +318,17 @@ int launch_hgrn2(const void* qfv, const void* bf, const float* lower, const floa
   const int col_blocks = fuse ? 1 : (dv + cols - 1) / cols;
   const size_t smem = ((size_t)3 * HG_TT * gate_row + (fuse ? 2 : 1) * (size_t)HG_TT * cols) * sizeof(float);
   dim3 grid(heads * col_blocks, B, chunks);
-  if (fuse)
-    return launch_kernel(hgrn2_scan_kernel<T, R, PARTS, true, 0, false>, grid, dim3(threads), smem, stream, (const T*)qfv, (const T*)bf,
-                         lower, nw, state, cu_q, state_slots, (T*)out, raw, ends, gates, heads, dk, dv, col_blocks, eps, num_slots, err);
-  if (dk == R * PARTS)
-    return launch_kernel(hgrn2_scan_kernel<T, R, PARTS, false, MODE, true>, grid, dim3(threads), smem, stream, (const T*)qfv,
-                         (const T*)bf, lower, nw, state, cu_q, state_slots, (T*)out, raw, ends, gates, heads, dk, dv, col_blocks, eps,
-                         num_slots, err);
-  return launch_kernel(hgrn2_scan_kernel<T, R, PARTS, false, MODE, false>, grid, dim3(threads), smem, stream, (const T*)qfv,
-                       (const T*)bf, lower, nw, state, cu_q, state_slots, (T*)out, raw, ends, gates, heads, dk, dv, col_blocks, eps,
-                       num_slots, err);
+  auto launch = [&](auto kernel) -> int {
+    if (smem > 48 * 1024) {      // a head of 256 gates: three rows of gates for 16 tokens pass the default limit
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    return launch_kernel(kernel, grid, dim3(threads), smem, stream, (const T*)qfv, (const T*)bf, lower, nw, state, cu_q, state_slots,
+                         (T*)out, raw, ends, gates, heads, dk, dv, col_blocks, eps, num_slots, err);
+  };
+  if (fuse) return launch(hgrn2_scan_kernel<T, R, PARTS, true, 0, false>);
+  if (dk == R * PARTS) return launch(hgrn2_scan_kernel<T, R, PARTS, false, MODE, true>);
+  return launch(hgrn2_scan_kernel<T, R, PARTS, false, MODE, false>);
 }
 
 // rows of the state a thread keeps, and lanes that share a column: from dk alone
