@@ -288,3 +288,55 @@ def test_the_command_line(folders):
                         "--num-kv-blocks", "16"], capture_output=True, text=True, timeout=1200)
     assert p.returncode == 0, p.stderr[-2000:]
     assert [int(t) for t in p.stdout.split()] == plain_greedy(folders, name, prompt, 6)
+
+
+def random_config(rng):
+    """Sizes drawn at random, odd ones among them: no size of the design may rest on another, or on being even or a power of two.
+    Cache rows (kv_rank + rot_dim, padded to 16) are held to three widths so that bfloat16 needs no further attention libraries."""
+    width = rng.choice([34, 50, 72, 96, 110, 136])
+    layers, writers = [], []
+    kinds = ["mingru", "hgrn2", "latent_attention", "latent_attention"] + [rng.choice(["mingru", "hgrn2", "latent_attention"]) for _ in range(rng.randint(0, 3))]
+    rng.shuffle(kinds)
+    for i, kind in enumerate(kinds):
+        ff = rng.choice([None, rng.randint(20, 150)])
+        if kind == "mingru":
+            m = dict(width=rng.randint(9, 200))
+        elif kind == "hgrn2":
+            m = dict(heads=rng.randint(1, 4), dim=rng.randint(3, 70), vdim=rng.randint(3, 140))
+        else:
+            src = rng.choice(writers) if writers and rng.random() < 0.5 else None
+            if src is None:
+                row = rng.choice([48, 64, 128])
+                rot_dim = 2 * rng.randint(1, 8)
+                kv_rank = row - rot_dim - rng.randint(0, 6)
+                rot = _rot(2 * rng.randint(1, rot_dim // 2), rng.choice([100.0, 10000.0, 777.0]),
+                           rng.choice([None, (rng.choice([2.0, 3.5, 16.0]), rng.choice([8, 32, 100]), rng.choice([4.0, 32.0]), rng.choice([1.0, 2.0]))]))
+                writers.append(i)
+            else:
+                other = layers[src]["mixer"]
+                rot_dim, kv_rank, rot = other["rot_dim"], other["kv_rank"], other["rot"]
+            m = _latent(rng.randint(1, 7), rng.randint(2, 40), rot_dim, rng.randint(2, 50), rng.randint(5, 60), kv_rank,
+                        rng.choice([0.05, 0.2, 0.5]), rot, window=rng.choice([None, 1, 2, 17, 40, 64]), kv_from=src)
+        layers.append(_layer(kind, m, ff))
+    cfg = {"architecture": "Tofilorn", "vocab": rng.randint(30, 300), "width": width, "norm": {"eps": rng.choice([1e-5, 1e-6])}, "layers": layers}
+    if rng.random() < 0.8:
+        cfg["streams"] = rng.randint(1, 6)
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_configurations_and_cuts(seed, tmp_path):
+    from vllm_oxide_b200.engine.loading import write_random_model_folder
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    rng = random.Random(1000 + seed)
+    cfg = random_config(rng)
+    write_random_model_folder(str(tmp_path), cfg, seed, "fan_in", torch.float32)
+    _, w = P.read_folder(str(tmp_path))
+    toks = [rng.randrange(cfg["vocab"]) for _ in range(75)]
+    for dtype in DTYPES:
+        wd = w if dtype == "float32" else {k: (v.to(torch.bfloat16).to(v.dtype) if v.dtype.is_floating_point and "hc" not in k
+                                               and "lower" not in k and "norm" not in k else v) for k, v in w.items()}
+        want = P.forward(cfg, wd, toks, torch.float64)[0].numpy()
+        r = TraceRunner(str(tmp_path), dtype, 128, rng.choice([16, 32, 64]), max_live=2)
+        for cuts in ([75], [rng.randint(1, 9) for _ in range(5)], [60] + [1] * 15):
+            close(feed(r, "x", toks, cuts), want, dtype, f"seed {seed} {dtype} cuts {cuts}: {json.dumps(cfg)[:300]}")
