@@ -265,3 +265,119 @@ class TofilornConfig:
         if self.streams is not None:
             d["streams"] = self.streams
         return d
+
+
+# ---------------------------------------------------------------------------------------------------------------
+_KESOZEN_MIXERS = ("attention", "delta")
+
+
+@dataclass(frozen=True)
+class KesozenLayer:
+    type: str                   # "attention" | "delta"
+    mixer: dict                 # the mixer's sizes and constants, as config.json gives them
+    mlp: Optional[dict]         # None, {"kind": "dense", "ff"} or {"kind": "moe", "expert": {"ff"}, "router": {...}}
+
+
+@dataclass(frozen=True)
+class KesozenConfig:
+    """Kesozen: a decoder whose layers are listed one by one in config.json, each with a norm before and after both of
+    its sublayers around one float residual stream.  The mixer is attention whose keys double as values (a sink in the
+    softmax, a gate per head, part of each head rotated) or a gated delta rule behind short convolutions; the
+    feed-forward is dense or a mixture of experts chosen among groups, both with the squared relu.  A stretch of the
+    layers (`loop`: start, stop, times) may run several times in a row with the same weights, every pass with a cache of
+    its own, the normed embedding added back before each pass but the first.  Keys: `vocab`, `width`, `norm.eps`,
+    `layers[i]` = {type, mixer{...}, mlp}, `loop`.  There is no largest position."""
+    vocab: int
+    width: int
+    eps: float
+    layers: tuple
+    loop: Optional[tuple] = None      # (start, stop, times)
+    torch_dtype: str = "bfloat16"
+
+    architecture = "Kesozen"
+
+    @classmethod
+    def from_dict(cls, d: dict, where: str = "config.json") -> "KesozenConfig":
+        layers = d.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError(f"{where}: 'layers' must be a non-empty list")
+        out = []
+        for i, layer in enumerate(layers):
+            w = f"{where}: layers[{i}]"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"{w} must be an object")
+            kind = layer.get("type")
+            if kind not in _KESOZEN_MIXERS:
+                raise ConfigError(f"{w}: type {kind!r} is not one of {list(_KESOZEN_MIXERS)}")
+            m = _sub(layer, "mixer", w)
+            for k in ("heads", "kv_heads", "dim", "vdim"):
+                _need(m, k, int, w)
+            if m["heads"] % m["kv_heads"]:
+                raise ConfigError(f"{w}: heads {m['heads']} is not a multiple of kv_heads {m['kv_heads']}")
+            if kind == "attention":
+                _need(m, "scale", float, w)
+                if m["vdim"] != m["dim"]:
+                    raise ConfigError(f"{w}: the values are the keys, so vdim {m['vdim']} must equal dim {m['dim']}")
+                rot = m.get("rot")
+                if rot is not None:
+                    rot = _sub(m, "rot", w)
+                    _need(rot, "base", float, w + ".rot")
+                    dims = rot.get("dims")
+                    if isinstance(dims, bool) or not isinstance(dims, int) or dims < 0 or dims % 2 or dims > m["dim"]:
+                        raise ConfigError(f"{w}: rot.dims {dims!r} must be even and between 0 and dim {m['dim']}")
+            else:
+                _need(m, "conv", int, w)
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict) or mlp.get("kind") not in ("dense", "moe"):
+                    raise ConfigError(f"{w}: mlp must be null or of kind 'dense' or 'moe', got {mlp!r}")
+                if mlp["kind"] == "dense":
+                    _need(mlp, "ff", int, w + ".mlp")
+                else:
+                    _need(_sub(mlp, "expert", w + ".mlp"), "ff", int, w + ".mlp.expert")
+                    r = _sub(mlp, "router", w + ".mlp")
+                    E, top = _need(r, "experts", int, w + ".mlp.router"), _need(r, "top", int, w + ".mlp.router")
+                    g = r.get("groups")
+                    count = keep = 1
+                    if g is not None:
+                        g = _sub(r, "groups", w + ".mlp.router")
+                        count, keep = _need(g, "count", int, w + ".mlp.router.groups"), _need(g, "keep", int, w + ".mlp.router.groups")
+                    if E % count or keep > count or top > (E // count) * keep:
+                        raise ConfigError(f"{w}: {E} experts in {count} groups of which {keep} are kept cannot give {top} choices")
+            out.append(KesozenLayer(kind, dict(m), None if mlp is None else dict(mlp)))
+        loop = d.get("loop")
+        if loop is not None:
+            loop = _sub(d, "loop", where)
+            start, stop = loop.get("start"), loop.get("stop")
+            times = _need(loop, "times", int, where + ".loop")
+            for v in (start, stop):
+                if isinstance(v, bool) or not isinstance(v, int):
+                    raise ConfigError(f"{where}: loop.start and loop.stop must be integers")
+            if not 0 <= start <= stop <= len(out):
+                raise ConfigError(f"{where}: loop {start}..{stop} does not lie within the {len(out)} layers")
+            loop = (start, stop, times)
+        dtype = d.get("torch_dtype", d.get("dtype", "bfloat16"))
+        if not isinstance(dtype, str) or dtype not in _DTYPE_NAMES:
+            raise ConfigError(f"{where}: torch_dtype {dtype!r} is not one of {sorted(set(_DTYPE_NAMES))}")
+        return cls(vocab=_need(d, "vocab", int, where), width=_need(d, "width", int, where),
+                   eps=_need(_sub(d, "norm", where), "eps", float, where + ".norm"), layers=tuple(out), loop=loop,
+                   torch_dtype=_DTYPE_NAMES[dtype])
+
+    def runs(self):
+        """The layers in the order they run: [(layer, first of a pass after the first)]."""
+        n = len(self.layers)
+        if self.loop is None:
+            return [(i, False) for i in range(n)]
+        start, stop, times = self.loop
+        order = [(i, False) for i in range(start)]
+        for rep in range(times):
+            order += [(i, rep > 0 and i == start) for i in range(start, stop)]
+        return order + [(i, False) for i in range(stop, n)]
+
+    def to_dict(self) -> dict:
+        d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.eps},
+             "layers": [{"type": l.type, "mixer": dict(l.mixer), "mlp": None if l.mlp is None else dict(l.mlp)}
+                        for l in self.layers]}
+        if self.loop is not None:
+            d["loop"] = {"start": self.loop[0], "stop": self.loop[1], "times": self.loop[2]}
+        return d

@@ -58,7 +58,8 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
                                const int* __restrict__ block_tables, int table_stride,
                                const int* __restrict__ token_req, const int* __restrict__ positions,
                                const int* __restrict__ skip_single_cu_q, int nh, int kvh, int hd, int vd, int block_size,
-                               int window, float scale, long num_pages, int* err) {
+                               int window, float scale, long num_pages, int sink, const T* gate, long gate_stride,
+                               int* err) {
   extern __shared__ float smem[];
   float* qs = smem;                        // [hd]
   float* accs = smem + hd;                 // [ATT_WARPS][hd]
@@ -123,18 +124,22 @@ paged_attention_generic_kernel(const T* q, long q_stride, T* out,
   float mm = -INFINITY;
 #pragma unroll
   for (int w = 0; w < ATT_WARPS; ++w) mm = fmaxf(mm, ms[w]);
-  float f[ATT_WARPS], lt = 0.f;
+  // a sink is one more entry of score 0 that has no value: it adds exp(0 - max) to the denominator and nothing else
+  if (sink) mm = fmaxf(mm, 0.f);
+  float f[ATT_WARPS], lt = sink ? expf(-mm) : 0.f;
 #pragma unroll
   for (int w = 0; w < ATT_WARPS; ++w) {
     f[w] = (ms[w] == -INFINITY) ? 0.f : expf(ms[w] - mm);
     lt += ls[w] * f[w];
   }
+  // a gate: the head's output times sigmoid of one number of the token's row
+  const float gt = gate ? 1.f / (1.f + expf(-to_f<T>(gate[(size_t)t * gate_stride + h]))) : 1.f;
   T* orow = out + (size_t)t * nh * vd + (size_t)h * vd;
   for (int d = threadIdx.x; d < vd; d += blockDim.x) {
     float o = 0.f;
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) o += accs[w * hd + d] * f[w];
-    orow[d] = from_f<T>(lt > 0.f ? o / lt : 0.f);
+    orow[d] = from_f<T>(lt > 0.f ? o / lt * gt : 0.f);
   }
 }
 
@@ -144,13 +149,15 @@ using namespace vob;
 
 // q: rows of q_stride elements, head h at h*hd; out [T, nh*vd]; caches [num_pages, kvh, block_size, hd];
 // block_tables [B, table_stride]; token_req [T] (-1: padding); positions [T].  Of a value row the first vd elements are
-// read (vd = hd: all of it; less when keys and values are one row and the key is the longer one).
+// read (vd = hd: all of it; less when keys and values are one row and the key is the longer one).  `sink`: the softmax
+// has a silent extra entry of score 0 (weights exp(s) / (1 + sum exp(s))); `gate` (rows of gate_stride elements, one
+// number a head): head h of token t is multiplied by sigmoid(gate[t, h]).
 VOB_API int vob_paged_attention_generic(const void* q, long q_stride, void* out, const void* kcache, const void* vcache,
                                         const int* block_tables, int table_stride, const int* token_req,
                                         const int* positions, const int* skip_single_cu_q, int T, int nh, int kvh, int hd,
                                         int vd, int block_size,
-                                        int window, float scale, long num_pages, int dtype, int* err,
-                                        cudaStream_t stream) {
+                                        int window, float scale, long num_pages, int sink, const void* gate,
+                                        long gate_stride, int dtype, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd <= 0 || hd % 16 || hd > 512 || kvh <= 0 || nh % kvh || block_size <= 0 || vd <= 0 || vd > hd) return VOB_UNSUPPORTED;
   dim3 grid(T, nh);
@@ -158,11 +165,13 @@ VOB_API int vob_paged_attention_generic(const void* q, long q_stride, void* out,
   if (dtype == VOB_F32)
     return launch_kernel(paged_attention_generic_kernel<float>, grid, ATT_WARPS * 32, smem, stream, (const float*)q, q_stride,
                          (float*)out, (const float*)kcache, (const float*)vcache, block_tables, table_stride, token_req,
-                         positions, skip_single_cu_q, nh, kvh, hd, vd, block_size, window, scale, num_pages, err);
+                         positions, skip_single_cu_q, nh, kvh, hd, vd, block_size, window, scale, num_pages, sink,
+                         (const float*)gate, gate_stride, err);
   if (dtype == VOB_BF16)
     return launch_kernel(paged_attention_generic_kernel<__nv_bfloat16>, grid, ATT_WARPS * 32, smem, stream,
                          (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache,
                          (const __nv_bfloat16*)vcache, block_tables, table_stride, token_req, positions, skip_single_cu_q,
-                         nh, kvh, hd, vd, block_size, window, scale, num_pages, err);
+                         nh, kvh, hd, vd, block_size, window, scale, num_pages, sink, (const __nv_bfloat16*)gate,
+                         gate_stride, err);
   return VOB_BAD_ARGUMENT;
 }

@@ -1,0 +1,317 @@
+// A mixture of experts inside a feed-forward: routing, the experts' products over tokens sorted by expert, the weighted sum.
+//
+//   moe_route     z = W_r h in float (one chain of additions a logit, whatever the batch), s = softmax(z) over all experts;
+//                 the choice is by s + correction, among the experts of the `keep` groups (of `count` equal groups of
+//                 neighbours) whose best choice score is largest; the `top` best are taken and weighted by their plain s,
+//                 as it is (no renormalisation).  Ties go to the lower index.
+//   moe_align     sorts the step's (token, choice) pairs by expert: every expert's rows start on a multiple of the product's
+//                 row tile (padding rows name no token), and each row tile knows its expert.  Everything stays on the
+//                 device: the grid of the products is sized for the worst case and tiles past the end return at once.
+//   moe_gemm      C[row] = f(A[row] W_e^T) for the rows of expert e, W stacked [experts, N, K]; A is either gathered by the
+//                 row's token (the first product) or read in place (the second); f is the identity or the squared relu.
+//                 Float accumulation, one chain of fused multiply-adds over k in ascending order for every output element
+//                 (the float path's product, with a tile's expert in front of it).
+//   moe_combine   out[t] = sum_j weight[t, j] * y[row of (t, j)], j in order, in float.
+//   relu_squared  out = max(x, 0)^2 (the dense feed-forward's activation).
+#include "common.cuh"
+
+namespace vob {
+
+constexpr int MOE_TM = 64;       // rows of a product tile; experts' row ranges are padded to it
+
+// ---------------------------------------------------------------- routing
+struct Best { float v; int i; };
+__device__ __forceinline__ Best better(Best a, Best b) { return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a; }
+__device__ __forceinline__ Best warp_best(Best x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best y;
+    y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+    x = better(x, y);
+  }
+  return x;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __restrict__ correction, int* ids, float* weights,
+                 int W, int E, int top, int count, int keep) {
+  extern __shared__ float route_smem[];
+  float* hrow = route_smem;          // [W]
+  float* score = hrow + W;           // [E] softmax
+  float* choice = score + E;         // [E] score + correction, -inf once taken or shut out
+  float* gbest = choice + E;         // [count]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int d = threadIdx.x; d < W; d += 128) hrow[d] = to_f<T>(h[(size_t)t * W + d]);
+  __syncthreads();
+  for (int e = warp; e < E; e += 4) {
+    const float* wr = w_router + (size_t)e * W;
+    float z = 0.f;
+    for (int d = lane; d < W; d += 32) z = fmaf(hrow[d], wr[d], z);
+    z = warp_sum(z);
+    if (lane == 0) score[e] = z;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float m = -INFINITY;
+  for (int e = lane; e < E; e += 32) m = fmaxf(m, score[e]);
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) sum += expf(score[e] - m);
+  sum = warp_sum(sum);
+  for (int e = lane; e < E; e += 32) {
+    const float s = expf(score[e] - m) / sum;
+    score[e] = s;
+    choice[e] = s + correction[e];
+  }
+  __syncwarp();
+  const int per = E / count;
+  if (keep < count) {
+    for (int g = lane; g < count; g += 32) {
+      float b = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, choice[e]);
+      gbest[g] = b;
+    }
+    __syncwarp();
+    // the `keep` best groups are marked by +inf; then every expert of an unmarked group is shut out
+    for (int it = 0; it < keep; ++it) {
+      Best x{-INFINITY, 0x7fffffff};
+      for (int g = lane; g < count; g += 32)
+        if (gbest[g] != INFINITY) x = better(x, Best{gbest[g], g});
+      x = warp_best(x);
+      __syncwarp();
+      if (lane == 0 && x.i < count) gbest[x.i] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (gbest[e / per] != INFINITY) choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  for (int j = 0; j < top; ++j) {
+    Best x{-INFINITY, 0x7fffffff};
+    for (int e = lane; e < E; e += 32) x = better(x, Best{choice[e], e});
+    x = warp_best(x);
+    __syncwarp();
+    if (lane == 0) {
+      const int e = x.i < E ? x.i : 0;
+      ids[(size_t)t * top + j] = e;
+      weights[(size_t)t * top + j] = x.i < E ? score[e] : 0.f;
+      choice[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------- sorting by expert
+// One block.  n = tokens * top pairs; slot_of[n]: the row of a pair; row_token[max_rows]: a row's token (-1: padding);
+// tile_expert[max_rows / MOE_TM]: a row tile's expert (-1: past the end).
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int* ids, int* slot_of, int* row_token, int* tile_expert, int n, int top, int E, int max_rows) {
+  extern __shared__ int align_smem[];
+  int* counts = align_smem;          // [E]
+  int* offsets = counts + E;         // [E]
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  for (int r = threadIdx.x; r < max_rows; r += blockDim.x) row_token[r] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = off;
+      const int padded = (counts[e] + MOE_TM - 1) / MOE_TM * MOE_TM;
+      for (int tile = off / MOE_TM; tile < (off + padded) / MOE_TM; ++tile) tile_expert[tile] = e;
+      off += padded;
+      counts[e] = 0;      // now the expert's cursor
+    }
+    for (int tile = off / MOE_TM; tile < max_rows / MOE_TM; ++tile) tile_expert[tile] = -1;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = ids[i];
+    if (e < 0 || e >= E) { slot_of[i] = -1; continue; }
+    const int row = offsets[e] + atomicAdd(&counts[e], 1);
+    slot_of[i] = row;
+    row_token[row] = i / top;
+  }
+}
+
+// ---------------------------------------------------------------- the experts' products
+constexpr int MG_N = 64, MG_K = 16;
+
+// EPI 0: as it is; 1: squared relu.  GATHER: row r of A is a[row_token[r]], else a[r].
+template <typename TA, typename TC, int EPI, bool GATHER>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const TA* A, long lda, const TA* __restrict__ W, TC* C, long ldc, const int* row_token,
+                const int* tile_expert, int N, int K) {
+  __shared__ float As[MG_K][MOE_TM + 4];
+  __shared__ float Ws[MG_K][MG_N + 4];
+  __shared__ int src[MOE_TM];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = tile_expert[blockIdx.y];
+  if (e < 0) return;
+  const int m0 = blockIdx.y * MOE_TM, n0 = blockIdx.x * MG_N;
+  const int tid = threadIdx.x;
+  if (tid < MOE_TM) {
+    const int tok = row_token[m0 + tid];
+    src[tid] = tok < 0 ? -1 : (GATHER ? tok : m0 + tid);
+  }
+  __syncthreads();
+  const TA* We = W + (size_t)e * N * K;
+  const int tx = tid % 16, ty = tid / 16;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const int lr = tid / 4, lk = (tid % 4) * 4;
+  const int arow = src[lr];
+  for (int k0 = 0; k0 < K; k0 += MG_K) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = k0 + lk + j;
+      const int wn = n0 + lr;
+      As[lk + j][lr] = (arow >= 0 && k < K) ? to_f<TA>(A[(size_t)arow * lda + k]) : 0.f;
+      Ws[lk + j][lr] = (wn < N && k < K) ? to_f<TA>(We[(size_t)wn * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < MG_K; ++k) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (src[ty * 4 + i] < 0) continue;
+    const int m = m0 + ty * 4 + i;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      float v = acc[i][j];
+      if (EPI == 1) { v = fmaxf(v, 0.f); v = v * v; }
+      C[(size_t)m * ldc + n] = from_f<TC>(v);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* y, const int* slot_of, const float* weights, T* out, int D, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int d = threadIdx.x; d < D; d += 256) {
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const int row = slot_of[(size_t)t * top + j];
+      if (row >= 0) acc = fmaf(weights[(size_t)t * top + j], y[(size_t)row * D + d], acc);
+    }
+    out[(size_t)t * D + d] = from_f<T>(acc);
+  }
+}
+
+template <typename T>
+__global__ void relu_squared_kernel(const T* x, T* out, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = fmaxf(to_f<T>(x[i]), 0.f);
+    out[i] = from_f<T>(v * v);
+  }
+}
+
+}  // namespace vob
+
+using namespace vob;
+
+VOB_API int vob_moe_row_tile() { return MOE_TM; }
+
+VOB_API int vob_moe_route(const void* h, const float* w_router, const float* correction, int* ids, float* weights, int T, int W,
+                          int E, int top, int count, int keep, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E || count <= 0 || E % count || keep <= 0 || keep > count || (long)(E / count) * keep < top)
+    return VOB_BAD_ARGUMENT;
+  const size_t smem = (size_t)(W + 2 * E + count) * sizeof(float);
+  if (smem > 200 * 1024) return VOB_UNSUPPORTED;
+#define VOB_ROUTE(TYPE)                                                                                                  \
+  do {                                                                                                                   \
+    if (smem > 48 * 1024)                                                                                                \
+      cudaFuncSetAttribute(moe_route_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
+    return launch_kernel(moe_route_kernel<TYPE>, dim3(T), 128, smem, stream, (const TYPE*)h, w_router, correction, ids,   \
+                         weights, W, E, top, count, keep);                                                               \
+  } while (0)
+  if (dtype == VOB_F32) VOB_ROUTE(float);
+  if (dtype == VOB_BF16) VOB_ROUTE(__nv_bfloat16);
+#undef VOB_ROUTE
+  return VOB_BAD_ARGUMENT;
+}
+
+VOB_API int vob_moe_align(const int* ids, int* slot_of, int* row_token, int* tile_expert, int n, int top, int E, int max_rows,
+                          cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (max_rows % MOE_TM || E <= 0 || E > 4096) return VOB_BAD_ARGUMENT;
+  return launch_kernel(moe_align_kernel, dim3(1), 1024, (size_t)2 * E * sizeof(int), stream, ids, slot_of, row_token, tile_expert,
+                       n, top, E, max_rows);
+}
+
+// A: rows of lda elements (`gather`: indexed by the row's token); W [experts, N, K]; C [max_rows, ldc] of `dtype`, or float
+// with `c_float`.  epilogue 0: as it is, 1: squared relu.
+VOB_API int vob_moe_gemm(const void* A, long lda, const void* W, void* C, long ldc, const int* row_token, const int* tile_expert,
+                         int max_rows, int N, int K, int epilogue, int gather, int c_float, int dtype, cudaStream_t stream) {
+  if (max_rows <= 0 || N <= 0) return 0;
+  if (K <= 0 || max_rows % MOE_TM) return VOB_BAD_ARGUMENT;
+  dim3 grid((N + MG_N - 1) / MG_N, max_rows / MOE_TM);
+  if (grid.y > 65535) return VOB_UNSUPPORTED;
+#define VOB_MG(TA, TC, EPI, G)                                                                                       \
+  return launch_kernel(moe_gemm_kernel<TA, TC, EPI, G>, grid, 256, 0, stream, (const TA*)A, lda, (const TA*)W, (TC*)C, ldc, \
+                       row_token, tile_expert, N, K)
+#define VOB_MG_TYPE(TA)                                                   \
+  if (epilogue == 1 && gather && !c_float) VOB_MG(TA, TA, 1, true);       \
+  if (epilogue == 0 && !gather && c_float) VOB_MG(TA, float, 0, false);   \
+  return VOB_UNSUPPORTED
+  if (dtype == VOB_F32) { VOB_MG_TYPE(float); }
+  if (dtype == VOB_BF16) { VOB_MG_TYPE(__nv_bfloat16); }
+#undef VOB_MG_TYPE
+#undef VOB_MG
+  return VOB_BAD_ARGUMENT;
+}
+
+VOB_API int vob_moe_combine(const float* y, const int* slot_of, const float* weights, void* out, int T, int D, int top, int dtype,
+                            cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (dtype == VOB_F32)
+    return launch_kernel(moe_combine_kernel<float>, dim3(T), 256, 0, stream, y, slot_of, weights, (float*)out, D, top);
+  if (dtype == VOB_BF16)
+    return launch_kernel(moe_combine_kernel<__nv_bfloat16>, dim3(T), 256, 0, stream, y, slot_of, weights, (__nv_bfloat16*)out, D, top);
+  return VOB_BAD_ARGUMENT;
+}
+
+VOB_API int vob_relu_squared(const void* x, void* out, long total, int dtype, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (dtype == VOB_F32)
+    return launch_kernel(relu_squared_kernel<float>, dim3(blocks), 256, 0, stream, (const float*)x, (float*)out, (size_t)total);
+  if (dtype == VOB_BF16)
+    return launch_kernel(relu_squared_kernel<__nv_bfloat16>, dim3(blocks), 256, 0, stream, (const __nv_bfloat16*)x,
+                         (__nv_bfloat16*)out, (size_t)total);
+  return VOB_BAD_ARGUMENT;
+}

@@ -202,17 +202,153 @@ def qk_norm_rope_kv_write(qkv, bias, positions, slots, wq, wk, rule, kcache, vca
 
 
 def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, token_req, positions, num_tokens, nh, kvh,
-                            hd, window: int, scale: float, err, skip_single_cu_q=None, value_dim: Optional[int] = None) -> None:
+                            hd, window: int, scale: float, err, skip_single_cu_q=None, value_dim: Optional[int] = None,
+                            sink: bool = False, gate=None, gate_stride: int = 0) -> None:
     """Every token of the batch; with `skip_single_cu_q` (the batch's cu_q) the tokens of requests that
     bring exactly one token are left to the decode kernel.  `value_dim`: only that many leading elements of a value
-    row are read and `out` is [tokens, nh * value_dim] (keys and values may then be one and the same plane)."""
-    _cuda(q, out, kcache, vcache, block_tables, token_req, positions)
+    row are read and `out` is [tokens, nh * value_dim] (keys and values may then be one and the same plane).
+    `sink`: the softmax has a silent extra entry of score 0; `gate` (a view whose element [t * gate_stride + h] is head
+    h's number for token t): every head's output is multiplied by the sigmoid of its number."""
+    _cuda(q, out, kcache, vcache, block_tables, token_req, positions, gate)
+    assert gate is None or gate.dtype == q.dtype
     _check(lib().vob_paged_attention_generic(_p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache),
                                              _p(block_tables), block_tables.shape[-1], _p(token_req), _p(positions),
                                              _p(skip_single_cu_q), num_tokens, nh, kvh, hd,
                                              hd if value_dim is None else int(value_dim), kcache.shape[2], window,
-                                             ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), _code(q.dtype),
-                                             _p(err), _stream()), "paged_attention_generic")
+                                             ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), int(bool(sink)), _p(gate),
+                                             ctypes.c_long(gate_stride), _code(q.dtype), _p(err), _stream()),
+           "paged_attention_generic")
+
+
+def rope_shared_kv_write(qk, positions, slots, rule, kcache, vcache, num_tokens: int, nh: int, kvh: int, hd: int,
+                         write_kv: bool, err) -> None:
+    """A merged q|k row of an attention whose values are its keys: query heads rotated in place, every key head written
+    as it is into `vcache` and rotated into `kcache` (planes [pages, kvh, page size, hd]).  `rule` must carry
+    `frequencies` (a position part made with table=False) and rotate in halves; rotary_dim 0 rotates nothing."""
+    _cuda(qk, positions, slots, rule.frequencies, kcache, vcache)
+    if rule.rotary_dim > 0 and (rule.frequencies is None or rule.interleaved or rule.amplitude != 1.0):
+        raise KernelError("rope_shared_kv_write rotates halves by computed angles: the rule needs `frequencies`, no "
+                          "interleaving and amplitude 1")
+    assert qk.stride(1) == 1 and kcache.dtype == qk.dtype == vcache.dtype and kcache.shape == vcache.shape
+    _check(lib().vob_rope_shared_kv_write(_p(qk), ctypes.c_long(qk.stride(0)), _p(positions), _p(slots), _p(rule.frequencies),
+                                          _p(kcache), _p(vcache), num_tokens, nh, kvh, hd, rule.rotary_dim,
+                                          ctypes.c_long(kcache.shape[0] * kcache.shape[2]), kcache.shape[2], int(write_kv),
+                                          _code(qk.dtype), _p(err), _stream()), "rope_shared_kv_write")
+
+
+def residual_norm_step(stream, eps: float, err, y=None, w_post=None, inject=None, keep=None, w_pre=None, out=None, rows=None,
+                       n_out: Optional[int] = None, init: bool = False) -> None:
+    """One pass over a float residual stream [tokens, width] with norms on both sides of a sublayer: x = 0 (`init`) or
+    the stream's row; x += RMSNorm(y) * w_post (w_post None: x += y); x += inject; the row is stored (and copied to `keep`);
+    out = RMSNorm(x) * w_pre.  With `rows` (source rows, `n_out` of them) only `out` is computed and nothing is stored."""
+    _cuda(stream, y, w_post, inject, keep, w_pre, out, rows)
+    assert stream.dtype == torch.float32 and stream.is_contiguous()
+    for t in (w_post, w_pre, inject, keep):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    act = next((t for t in (out, y) if t is not None), None)
+    for t in (y, out):
+        assert t is None or (t.dtype == act.dtype and t.is_contiguous() and t.shape[1] == stream.shape[1])
+    n_src = stream.shape[0]
+    n = n_src if rows is None else int(n_out)
+    _check(lib().vob_residual_norm_step(_p(stream), _p(y), _p(w_post), _p(inject), _p(keep), _p(w_pre), _p(out), _p(rows), n,
+                                        n_src, stream.shape[1], ctypes.c_float(eps), int(bool(init)),
+                                        _code(act.dtype if act is not None else torch.float32), _p(err), _stream()),
+           "residual_norm_step")
+
+
+def short_conv_silu(x, channels: int, taps_w, state, conv_off: int, token_req, cu_q, state_slots, out, num_tokens: int, err) -> None:
+    """out[t, c] = SiLU(sum_j taps_w[c, j] * x[t - (taps - 1) + j, c]) over every request's tokens of this step (float out
+    [tokens, channels]); the inputs before a portion's start come from the request's slot: state [slots, n] float, the
+    last taps - 1 inputs of every channel at conv_off.  x: the first `channels` columns of its rows."""
+    _cuda(x, taps_w, state, token_req, cu_q, state_slots, out)
+    assert x.stride(1) == 1 and taps_w.dtype == torch.float32 and taps_w.is_contiguous() and taps_w.shape[0] == channels
+    assert state.dtype == torch.float32 and state.is_contiguous() and out.dtype == torch.float32 and out.is_contiguous()
+    _check(lib().vob_short_conv_silu(_p(x), ctypes.c_long(x.stride(0)), _p(taps_w), _p(state), ctypes.c_long(state.stride(0)),
+                                     ctypes.c_long(conv_off), _p(token_req), _p(cu_q), _p(state_slots), _p(out), num_tokens,
+                                     channels, taps_w.shape[1], ctypes.c_long(state.shape[0]), _code(x.dtype), _p(err),
+                                     _stream()), "short_conv_silu")
+
+
+def short_conv_state(x, channels: int, taps: int, state, conv_off: int, cu_q, state_slots, num_requests: int) -> None:
+    """Leaves in every request's slot the last taps - 1 inputs of every channel after this step's portion (from the
+    portion, and from what the slot held where the portion is shorter).  Run after short_conv_silu."""
+    _cuda(x, state, cu_q, state_slots)
+    _check(lib().vob_short_conv_state(_p(x), ctypes.c_long(x.stride(0)), _p(state), ctypes.c_long(state.stride(0)),
+                                      ctypes.c_long(conv_off), _p(cu_q), _p(state_slots), num_requests, channels, taps,
+                                      ctypes.c_long(state.shape[0]), _code(x.dtype), _stream()), "short_conv_state")
+
+
+def delta_scan(qkv, ab, b_off: int, a_off: int, A_log, dt_bias, state, cu_q, state_slots, raw, num_requests: int, heads: int,
+               kvh: int, dim: int, vdim: int, err) -> None:
+    """The gated delta rule over every request's tokens of this step, from and to its slot (state [slots, n] float, the
+    heads' matrices [heads, dim, vdim] first).  qkv float [tokens, 2 kvh dim + heads vdim]; ab: rows whose elements
+    b_off + h and a_off + h are head h's pre-activations of beta and of the decay; raw float [tokens, heads * vdim]."""
+    _cuda(qkv, ab, A_log, dt_bias, state, cu_q, state_slots, raw)
+    assert qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[1] == 2 * kvh * dim + heads * vdim
+    assert raw.dtype == torch.float32 and raw.is_contiguous() and A_log.dtype == dt_bias.dtype == torch.float32
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] >= heads * dim * vdim and ab.stride(1) == 1
+    _check(lib().vob_delta_scan(_p(qkv), _p(ab), ctypes.c_long(ab.stride(0)), b_off, a_off, _p(A_log), _p(dt_bias), _p(state),
+                                ctypes.c_long(state.stride(0)), _p(cu_q), _p(state_slots), _p(raw), num_requests, heads, kvh,
+                                dim, vdim, ctypes.c_long(state.shape[0]), _code(ab.dtype), _p(err), _stream()), "delta_scan")
+
+
+def delta_out_norm(raw, gate, weight, out, num_tokens: int, heads: int, vdim: int, eps: float) -> None:
+    """out[t, h] = raw[t, h] / sqrt(mean(raw[t, h]^2) + eps) * weight * SiLU(gate[t, h]) per head over vdim; gate: the
+    first heads * vdim columns of its rows."""
+    _cuda(raw, gate, weight, out)
+    assert raw.dtype == torch.float32 and raw.is_contiguous() and out.is_contiguous() and gate.stride(1) == 1
+    assert weight.dtype == torch.float32 and gate.dtype == out.dtype
+    _check(lib().vob_delta_out_norm(_p(raw), _p(gate), ctypes.c_long(gate.stride(0)), _p(weight), _p(out), num_tokens, heads,
+                                    vdim, ctypes.c_float(eps), _code(out.dtype), _stream()), "delta_out_norm")
+
+
+def moe_row_tile() -> int:
+    """Rows of a tile of the experts' products: every expert's rows are padded to a multiple of it."""
+    return int(lib().vob_moe_row_tile())
+
+
+def moe_route(h, w_router, correction, ids, weights, num_tokens: int, top: int, groups: int, keep: int) -> None:
+    """ids, weights [tokens, top]: the experts a token uses and their softmax scores (see csrc/kernels/moe.cu)."""
+    _cuda(h, w_router, correction, ids, weights)
+    E, W = w_router.shape
+    assert h.is_contiguous() and h.shape[1] == W and w_router.dtype == correction.dtype == torch.float32
+    assert w_router.is_contiguous() and ids.dtype == torch.int32 and weights.dtype == torch.float32
+    _check(lib().vob_moe_route(_p(h), _p(w_router), _p(correction), _p(ids), _p(weights), num_tokens, W, E, top, groups, keep,
+                               _code(h.dtype), _stream()), "moe_route")
+
+
+def moe_align(ids, slot_of, row_token, tile_expert, n: int, top: int, experts: int) -> None:
+    """Sorts n (token, choice) pairs by expert: slot_of[n] a pair's row, row_token[rows] a row's token or -1, tile_expert
+    [rows / moe_row_tile()] a row tile's expert or -1."""
+    _cuda(ids, slot_of, row_token, tile_expert)
+    _check(lib().vob_moe_align(_p(ids), _p(slot_of), _p(row_token), _p(tile_expert), n, top, experts, row_token.numel(),
+                               _stream()), "moe_align")
+
+
+def moe_gemm(a, w, c, row_token, tile_expert, relu_squared: bool, gather: bool) -> None:
+    """c[row] = f(a[row or its token] @ w[expert of the row]^T), w [experts, N, K]; float accumulation in one chain."""
+    _cuda(a, w, c, row_token, tile_expert)
+    assert a.stride(1) == 1 and w.is_contiguous() and c.stride(1) == 1 and a.dtype == w.dtype
+    assert c.dtype == (a.dtype if relu_squared else torch.float32) and relu_squared == gather
+    _check(lib().vob_moe_gemm(_p(a), ctypes.c_long(a.stride(0)), _p(w), _p(c), ctypes.c_long(c.stride(0)), _p(row_token),
+                              _p(tile_expert), row_token.numel(), w.shape[1], w.shape[2], int(relu_squared), int(gather),
+                              int(not relu_squared),
+                              _code(a.dtype), _stream()), "moe_gemm")
+
+
+def moe_combine(y, slot_of, weights, out, num_tokens: int, top: int) -> None:
+    """out[t] = sum_j weights[t, j] * y[slot_of[t, j]] (float, j in order)."""
+    _cuda(y, slot_of, weights, out)
+    assert y.dtype == torch.float32 and y.is_contiguous() and out.is_contiguous()
+    _check(lib().vob_moe_combine(_p(y), _p(slot_of), _p(weights), _p(out), num_tokens, out.shape[1], top, _code(out.dtype),
+                                 _stream()), "moe_combine")
+
+
+def relu_squared(x, out) -> None:
+    """out = max(x, 0)^2, element by element (out may be x)."""
+    _cuda(x, out)
+    assert x.is_contiguous() and out.is_contiguous() and x.dtype == out.dtype
+    _check(lib().vob_relu_squared(_p(x), _p(out), ctypes.c_long(x.numel()), _code(x.dtype), _stream()), "relu_squared")
 
 
 def stream_step(streams, num_streams: int, width: int, eps: float, err, y=None, init=None, mix=None, out_w=None, in_w=None,

@@ -32,8 +32,14 @@ class CausalLM:
         common = dict(positions=self.positions, dtype=dtype, device=device)
         self.blocks = [build_part("block", spec, **common) for spec in plan.layers]
         self.final_norm = build_part("norm", plan.final_norm, **common)
+        # a norm of the embedded tokens opens the residual stream; it keeps a copy of its output if a run adds it back later
+        self.embedding_norm = build_part("norm", plan.embedding_norm, **common) if plan.embedding_norm is not None else None
+        self._reinjects = any(s.reinject for s in plan.order)
+        if self._reinjects and self.embedding_norm is None:
+            raise ValueError("a run that adds the embedding's output back needs the plan's embedding norm, which keeps it")
         self.graph_safe = (all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
-                           and all(p.graph_safe for p in self.positions.values()))
+                           and all(p.graph_safe for p in self.positions.values())
+                           and (self.embedding_norm is None or self.embedding_norm.graph_safe))
         self.embedding = None
         self.lm_head = None
         self.planes: List[Optional[CachePlane]] = [None] * plan.num_planes()
@@ -54,6 +60,8 @@ class CausalLM:
         for b in self.blocks:
             specs += b.tensor_specs()
         specs += self.final_norm.tensor_specs()
+        if self.embedding_norm is not None:
+            specs += self.embedding_norm.tensor_specs()
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -65,6 +73,8 @@ class CausalLM:
         for b in self.blocks:
             b.load({s.name: tensors[s.name] for s in b.tensor_specs()})
         self.final_norm.load({s.name: tensors[s.name] for s in self.final_norm.tensor_specs()})
+        if self.embedding_norm is not None:
+            self.embedding_norm.load({s.name: tensors[s.name] for s in self.embedding_norm.tensor_specs()})
 
     def cache_specs(self) -> List[Optional[CacheSpec]]:
         """Per plane: what its writer's mixer keeps in pages (None: nothing)."""
@@ -89,6 +99,8 @@ class CausalLM:
         """Bytes of every distinct weight tensor (a tied output matrix counts once)."""
         seen, total = set(), 0
         tensors = [self.embedding, self.lm_head] + self.final_norm.device_tensors()
+        if self.embedding_norm is not None:
+            tensors += self.embedding_norm.device_tensors()
         for part in self.positions.values():
             tensors += part.device_tensors()
         for b in self.blocks:
@@ -107,9 +119,12 @@ class CausalLM:
         for part in self.positions.values():
             part.embed(hidden, ctx)
         residual = None
+        if self.embedding_norm is not None:
+            hidden, residual = self.embedding_norm.open_stream(hidden, ctx, keep=self._reinjects)
         order = self.plan.order
         ctx.prenormed = None
         for i, s in enumerate(order):
+            ctx.reinject = s.reinject
             plane = self.planes[s.plane] if s.plane is not None else None
             state = self.states[s.plane] if s.plane is not None else None
             # a hint for blocks that can use it: the first norm of the block that runs next (its arithmetic may be done
@@ -117,6 +132,7 @@ class CausalLM:
             ctx.next_norm = getattr(self.blocks[order[i + 1].layer], "input_norm", None) if i + 1 < len(order) else None
             hidden, residual = self.blocks[s.layer].forward(hidden, residual, ctx, plane, state, s.write_cache)
         ctx.next_norm = ctx.prenormed = None
+        ctx.reinject = False
         return hidden, residual
 
     def compute_logits(self, hidden, residual, ctx) -> torch.Tensor:

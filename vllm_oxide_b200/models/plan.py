@@ -5,7 +5,8 @@ plan.  Everything here is data: the layers are a list of block specs (each may c
 different mixer, feed-forward or norm), and the order in which they run is a list too.
 An `ExecStep` names a layer and the cache plane it uses; the same layer may be named twice
 (each run with a plane of its own), and a step with `write_cache=False` reads the plane
-that another step wrote.
+that another step wrote.  A step with `reinject` has the embedding's output added to the
+residual stream again before it runs.
 """
 from __future__ import annotations
 
@@ -20,6 +21,8 @@ class ExecStep:
     layer: int
     plane: Optional[int]        # cache plane / state index this run uses; None: the mixer keeps nothing
     write_cache: bool = True    # False: read what another run wrote into `plane`
+    reinject: bool = False      # True: the embedding's output (after the plan's embedding norm) is added to the residual
+                                # stream once more right before this run (a stretch of layers that runs again)
 
 
 @dataclass
@@ -38,6 +41,7 @@ class ModelPlan:
     default_dtype: str = "bfloat16"
     embedding_scale: float = 1.0           # the embedded tokens are multiplied by it
     logit_softcap: float = 0.0             # > 0: logits = cap * tanh(logits / cap)
+    embedding_norm: Optional[PartSpec] = None   # a norm of the embedded tokens; it opens the residual stream (`open_stream`)
 
     def num_planes(self) -> int:
         return 1 + max((s.plane for s in self.order if s.plane is not None), default=-1)

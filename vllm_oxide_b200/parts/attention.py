@@ -138,18 +138,84 @@ class Attention(Mixer):
                      self.scale, self._pairs)
 
 
+class SharedKVAttention(Mixer):
+    """Grouped-query attention whose values are its keys as projected: there is no value matrix, and the rotation (of the
+    first `rotary_dim` elements of every head, in halves, by angles computed from the position) touches the keys that are
+    scored but not the keys that are summed.  Options: `scale` (the score's factor, given, not derived from the head
+    size); `sink` (the softmax has a silent extra entry of score 0: weights exp(s) / (1 + sum exp(s))); `gate` (head h's
+    output is multiplied by sigmoid((W_g x)_h), W_g [heads, hidden] reading the same input as q and k).  q, k and the gate
+    are one product; the cache plane holds the rotated key as its key tensor and the plain key as its value tensor.
+    Tensors: <prefix>q, k, g, o."""
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float, position: Optional[str],
+                 prefix: str, positions: dict, dtype, device, sink: bool = True, gate: bool = True, window: Optional[int] = None,
+                 names=("q", "k", "g", "o"), **_):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
+        if head_dim % 16 or head_dim > 512:
+            raise ValueError(f"head_dim {head_dim} is not supported by the attention kernels (a multiple of 16 up to 512)")
+        self.H, self.nh, self.kvh, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.scale, self.sink, self.gate, self.window = float(scale), bool(sink), bool(gate), int(window or 0)
+        if position is not None and position not in positions:
+            raise KeyError(f"the plan names position encoding {position!r}, but has only {sorted(positions)}")
+        self.rotation = positions[position].rotation_rule() if position is not None else NO_ROTATION
+        if self.rotation.rotary_dim > self.hd:
+            raise ValueError(f"the position rule rotates {self.rotation.rotary_dim} dimensions, a head has {self.hd}")
+        self.prefix, self.dtype, self.device = prefix, dtype, device
+        self.n_q, self.n_k, self.n_g, self.n_o = (prefix + n for n in names)
+        self.gate_off = (self.nh + self.kvh) * self.hd             # where the gates' columns begin in a merged row
+        self.width = self.gate_off + ((self.nh + 7) // 8 * 8 if self.gate else 0)   # rows stay 16-byte aligned
+        self.wqkg = self.wo = None
+        self._pairs = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        q, kv = self.nh * self.hd, self.kvh * self.hd
+        specs = [TensorSpec(self.n_q, (q, self.H), "matrix", self.H), TensorSpec(self.n_k, (kv, self.H), "matrix", self.H),
+                 TensorSpec(self.n_o, (self.H, q), "matrix", q)]
+        if self.gate:
+            specs.append(TensorSpec(self.n_g, (self.nh, self.H), "matrix", self.H))
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        rows = [tensors[self.n_q], tensors[self.n_k]]
+        if self.gate:
+            g = tensors[self.n_g]
+            rows += [g, g.new_zeros((self.width - self.gate_off - self.nh, self.H))]
+        self.wqkg = torch.cat(rows, dim=0).contiguous()
+        self.wo = tensors[self.n_o].contiguous()
+        if self.wo.is_cuda:
+            self._pairs = kernels.decode_pairs_counter(self.wo.device)
+
+    def cache_spec(self) -> CacheSpec:
+        return CacheSpec(self.kvh, self.hd, self.window)
+
+    def forward(self, x, ctx, cache, state=None, write_cache: bool = True):
+        T = x.shape[0]
+        qkg = linear(x, self.wqkg, ctx.ws.get("qkg", T, self.width, x.dtype), ctx)
+        kernels.rope_shared_kv_write(qkg, ctx.positions, ctx.slot_mapping[cache.group], self.rotation, cache.k, cache.v, T,
+                                     self.nh, self.kvh, self.hd, write_cache, ctx.err)
+        attn = ctx.ws.get("attn_out", T, self.nh * self.hd, x.dtype)
+        paged_attend(qkg, self.width, attn, cache.k, cache.v, cache.group, ctx, T, self.nh, self.kvh, self.hd, self.window,
+                     self.scale, self._pairs, sink=self.sink, gate=qkg[:, self.gate_off:] if self.gate else None,
+                     gate_stride=self.width)
+        return linear(attn, self.wo, ctx.ws.get("attn_proj", T, self.H, x.dtype), ctx)
+
+
 def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: int, kvh: int, hd: int, window: int,
-                 scale: float, pairs=None, value_dim=None) -> int:
+                 scale: float, pairs=None, value_dim=None, sink: bool = False, gate=None, gate_stride: int = 0) -> int:
     """Attention of every query of the step over the pages of `keys` / `values`; returns the width of a head in `out`.
     bfloat16: decoding requests (one token) go to the split-key tensor-core kernel, requests with a portion to the
     tensor-core kernel for portions.  The 32-bit path, and sizes those kernels refuse, go to the plain kernel.
     `value_dim` (keys and values are one plane whose rows begin with the value): the plain kernel reads and writes only
     that much of a value row; the tensor-core kernels take whole rows, and the caller uses the first `value_dim`
-    elements of each head of `out`."""
+    elements of each head of `out`.  `sink`: the softmax has a silent extra entry of score 0.  `gate`: a view whose element
+    [t, h] (rows `gate_stride` apart) is head h's gate of token t; its output is multiplied by the sigmoid of it."""
     tables = ctx.block_tables[group]
-    if not kernels.has_fast_attention(q.dtype, hd, nh // kvh):
+    if not kernels.has_fast_attention(q.dtype, hd, nh // kvh) or ((sink or gate is not None) and not FAST_SINK_AND_GATE):
         kernels.paged_attention_generic(q, q_stride, out, keys, values, tables, ctx.token_req, ctx.positions, T,
-                                        nh, kvh, hd, window, scale, ctx.err, value_dim=value_dim)
+                                        nh, kvh, hd, window, scale, ctx.err, value_dim=value_dim, sink=sink, gate=gate,
+                                        gate_stride=gate_stride)
         return hd if value_dim is None else value_dim
     B = ctx.launch_requests
     if ctx.num_decode > 0:
@@ -164,6 +230,9 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
                                   ctx.max_q, nh, kvh, hd, window, scale, ctx.err)
     return hd
 
+
+# Whether the tensor-core attention kernels take a softmax with a sink and a gate on the heads (else the plain kernel does).
+FAST_SINK_AND_GATE = False
 
 DECODE_BLOCKS_PER_SM = 2   # blocks of the decode attention kernel that fit an SM (its shared memory decides)
 
@@ -193,3 +262,4 @@ def decode_splits(num_requests: int, kv_heads: int, max_keys: int, num_sms: int)
 
 
 register_part("mixer", "attention", Attention)
+register_part("mixer", "attention_shared_kv", SharedKVAttention)

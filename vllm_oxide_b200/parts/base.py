@@ -155,6 +155,12 @@ class Norm(Part):
         `residual`, and the norm is of `residual` itself."""
         raise NotImplementedError
 
+    def open_stream(self, hidden, ctx, keep: bool = False):
+        """(hidden, residual) after this norm has been applied to the embedded tokens, as the first block takes them; the
+        norm may leave its arithmetic to that block's first kernel.  `keep`: the norm's output is also kept where runs
+        with `reinject` find it (`ctx.embedding_out`).  Only norms that a plan may name as its embedding norm have it."""
+        raise NotImplementedError(f"{type(self).__name__} cannot be a plan's embedding norm")
+
 
 @dataclass(frozen=True)
 class RotationRule:

@@ -1,0 +1,98 @@
+"""Feed-forwards with the squared relu: a dense one, and a mixture of experts chosen among groups.
+
+`ReluSquaredMLP`: down(max(up(x), 0)^2).
+
+`RoutedExperts`: `experts` such feed-forwards (<prefix>e<i>.up, <prefix>e<i>.down), of which a token uses `top`.
+Router logits z = W_r x are float (the input may be the model type's rounding of x), scores s = softmax(z) over all
+experts; the choice is by s + correction; the experts form `groups` equal groups of neighbours, a group counts by its
+best choice score and only experts of the `keep` best groups can be chosen; the chosen experts are weighted by their
+plain scores s, not renormalised, and the output is the weighted sum of their outputs.  Nothing outside sees the
+experts: the step's (token, choice) pairs are sorted by expert on the device, the experts' products run over the sorted
+rows (each expert's rows padded to a row tile), and a last kernel sums a token's rows in order.  No count leaves the
+device, so a step launches the same kernels whatever the router decides.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import kernels
+from ..weights.loader import TensorSpec
+from .base import FeedForward, register_part
+from .linear import linear
+
+
+class ReluSquaredMLP(FeedForward):
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, names=("up", "down"), **_):
+        self.H, self.I = int(hidden_size), int(intermediate_size)
+        self.n_up, self.n_down = (prefix + n for n in names)
+        self.wup = self.wdown = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.n_up, (self.I, self.H), "matrix", self.H), TensorSpec(self.n_down, (self.H, self.I), "matrix", self.I)]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.wup, self.wdown = tensors[self.n_up].contiguous(), tensors[self.n_down].contiguous()
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        act = linear(x, self.wup, ctx.ws.get("act", T, self.I, x.dtype), ctx)
+        kernels.relu_squared(act, act)
+        return linear(act, self.wdown, ctx.ws.get("mlp_out", T, self.H, x.dtype), ctx)
+
+
+class RoutedExperts(FeedForward):
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, expert_size: int, experts: int, top: int, prefix: str, groups: int = 1, keep: int = 1,
+                 names=("up", "down", "router", "correction"), **_):
+        self.H, self.I, self.E, self.top = int(hidden_size), int(expert_size), int(experts), int(top)
+        self.groups, self.keep, self.prefix = int(groups), int(keep), prefix
+        if self.E % self.groups or self.keep > self.groups or self.top > (self.E // self.groups) * self.keep:
+            raise ValueError(f"{self.E} experts in {self.groups} groups of which {self.keep} are kept cannot give {self.top} choices")
+        self.n_up, self.n_down, self.n_router, self.n_correction = names
+        self.wup = self.wdown = self.router = self.correction = None
+
+    def _expert(self, e: int, name: str) -> str:
+        return f"{self.prefix}e{e}.{name}"
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        specs = []
+        for e in range(self.E):
+            specs += [TensorSpec(self._expert(e, self.n_up), (self.I, self.H), "matrix", self.H),
+                      TensorSpec(self._expert(e, self.n_down), (self.H, self.I), "matrix", self.I)]
+        return specs + [TensorSpec(self.prefix + self.n_router, (self.E, self.H), "coefficient", self.H, init="normal"),
+                        TensorSpec(self.prefix + self.n_correction, (self.E,), "coefficient", init="small")]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.wup = torch.stack([tensors[self._expert(e, self.n_up)] for e in range(self.E)]).contiguous()
+        self.wdown = torch.stack([tensors[self._expert(e, self.n_down)] for e in range(self.E)]).contiguous()
+        self.router = tensors[self.prefix + self.n_router].contiguous()
+        self.correction = tensors[self.prefix + self.n_correction].contiguous()
+
+    def forward(self, x, ctx):
+        T, top = x.shape[0], self.top
+        n, tile = T * top, kernels.moe_row_tile()
+        # every expert's rows are padded to a row tile: at most tile - 1 rows for each expert that has any
+        max_rows = (n + min(self.E, n) * (tile - 1) + tile - 1) // tile * tile
+        ids = ctx.ws.get_flat("moe_ids", n, torch.int32)
+        weights = ctx.ws.get_flat("moe_weights", n, torch.float32)
+        slot_of = ctx.ws.get_flat("moe_slot_of", n, torch.int32)
+        row_token = ctx.ws.get_flat("moe_row_token", max_rows, torch.int32)
+        tile_expert = ctx.ws.get_flat("moe_tile_expert", max_rows // tile, torch.int32)
+        kernels.moe_route(x, self.router, self.correction, ids, weights, T, top, self.groups, self.keep)
+        kernels.moe_align(ids, slot_of, row_token, tile_expert, n, top, self.E)
+        act = ctx.ws.get_flat("moe_act", max_rows * self.I, x.dtype).view(max_rows, self.I)
+        kernels.moe_gemm(x, self.wup, act, row_token, tile_expert, relu_squared=True, gather=True)
+        y = ctx.ws.get_flat("moe_y", max_rows * self.H, torch.float32).view(max_rows, self.H)
+        kernels.moe_gemm(act, self.wdown, y, row_token, tile_expert, relu_squared=False, gather=False)
+        out = ctx.ws.get("mlp_out", T, self.H, x.dtype)
+        kernels.moe_combine(y, slot_of, weights, out, T, top)
+        return out
+
+
+register_part("feed_forward", "relu2_mlp", ReluSquaredMLP)
+register_part("feed_forward", "routed_experts", RoutedExperts)

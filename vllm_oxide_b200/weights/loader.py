@@ -36,7 +36,7 @@ class TensorSpec:
     shape: Tuple[int, ...]
     role: str = "matrix"      # "matrix" | "embedding" | "norm" | "bias" | "coefficient" (kept float) | "table" (integer)
     fan_in: Optional[int] = None
-    init: Optional[str] = None   # how random weights draw a coefficient: "one", "mean", "identity", "fraction"
+    init: Optional[str] = None   # how random weights draw a coefficient: "one", "mean", "identity", "fraction", "normal", "small"
 
 
 class WeightsError(ValueError):

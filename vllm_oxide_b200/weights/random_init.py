@@ -37,6 +37,10 @@ def random_tensor(spec: TensorSpec, seed: int, scheme: str, device, dtype: torch
             x = torch.eye(spec.shape[-1], device=device, dtype=torch.float32) + 0.05 * x
         elif spec.init == "fraction":
             x = torch.sigmoid(x)
+        elif spec.init == "normal":        # float matrices and vectors that are not near one: routers, filters, rates
+            x = x / (float(spec.fan_in) ** 0.5) if spec.fan_in else x
+        elif spec.init == "small":
+            x = 0.1 * x
         else:
             x = 1.0 + 0.1 * x
     elif spec.role == "norm":
