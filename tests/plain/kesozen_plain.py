@@ -141,26 +141,48 @@ def dense_ff(h, w, p, dt):
     return relu_squared(h @ w[p + "up"].to(dt).T) @ w[p + "down"].to(dt).T
 
 
-def route(h, w, p, r, dt):
+def route(h, w, p, r, dt, margins=None):
     """(chosen experts [n, top], their weights [n, top]).  Scores are a softmax over all experts; the choice is by score
     plus a correction, among the experts of the `keep` groups whose best choice score is largest; the weights are the
-    plain scores of the chosen, as they are."""
+    plain scores of the chosen, as they are.  `margins` (a list): a tensor [n] is appended, how far each token's choice
+    was from falling otherwise: the gap between the last group or expert taken and the first one left, as a share of
+    the two's plain scores times the spread of the token's logits."""
     E, top = int(r["experts"]), int(r["top"])
     groups = r.get("groups") or {"count": 1, "keep": 1}
     count, keep = int(groups["count"]), int(groups["keep"])
-    s = torch.softmax(h @ w[p + "router"].to(dt).T, dim=-1)
-    choice = s + w[p + "correction"].to(dt)
+    z = h @ w[p + "router"].to(dt).T
+    s = torch.softmax(z, dim=-1)
+    choice = choice_all = s + w[p + "correction"].to(dt)
     best = choice.reshape(-1, count, E // count).max(-1).values                     # [n, count]
     kept = torch.zeros_like(best, dtype=torch.bool)
     kept.scatter_(1, best.topk(keep, dim=-1).indices, True)
     allowed = kept[:, :, None].expand(-1, -1, E // count).reshape(-1, E)
     choice = torch.where(allowed, choice, torch.full_like(choice, -math.inf))
     idx = choice.topk(top, dim=-1).indices
+    if margins is not None:
+        # rounding moves a logit by a share of the logits' size, and a score by that times itself: the gap is measured
+        # against the two scores on either side of it times the spread of the token's logits
+        n = h.shape[0]
+        ratio = torch.full((n,), math.inf, dtype=dt)
+        spread = z.std(-1) if E > 1 else torch.ones(n, dtype=dt)
+        if keep < count:
+            per = E // count
+            first = choice_all.reshape(n, count, per).argmax(-1) + torch.arange(count) * per       # each group's best expert
+            order = best.argsort(-1, descending=True)
+            a, b = order[:, keep - 1:keep], order[:, keep:keep + 1]
+            gap = (best.gather(1, a) - best.gather(1, b))[:, 0]
+            ratio = torch.minimum(ratio, gap / ((s.gather(1, first.gather(1, a)) + s.gather(1, first.gather(1, b)))[:, 0] * spread))
+        if top < (E // count) * keep:
+            order = choice.argsort(-1, descending=True)
+            a, b = order[:, top - 1:top], order[:, top:top + 1]
+            gap = (choice.gather(1, a) - choice.gather(1, b))[:, 0]
+            ratio = torch.minimum(ratio, gap / ((s.gather(1, a) + s.gather(1, b))[:, 0] * spread))
+        margins.append(ratio)
     return idx, s.gather(1, idx)
 
 
-def moe_ff(h, w, p, mlp, dt):
-    idx, weight = route(h, w, p, mlp["router"], dt)
+def moe_ff(h, w, p, mlp, dt, margins=None):
+    idx, weight = route(h, w, p, mlp["router"], dt, margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(idx.shape[1]):
@@ -184,9 +206,13 @@ def layer_runs(cfg):
     return runs + [(i, False) for i in range(b, n)]
 
 
-def forward(cfg, w, tokens, dt=torch.float64, return_layers=False):
-    """Logits [n, vocab] for one whole sequence; with `return_layers` also the residual stream after every layer run."""
+def forward(cfg, w, tokens, dt=torch.float64, return_layers=False, margins=None, noise=None):
+    """Logits [n, vocab] for one whole sequence; with `return_layers` also the residual stream after every layer run.
+    `margins` (a list): every run of a routed feed-forward appends its tokens' margins (see `route`).  `noise` (a
+    function of a tensor): applied to what every sublayer reads and returns, e.g. a rounding to 16 bits, to see how far
+    rounding alone moves a row."""
     eps = float(cfg["norm"]["eps"])
+    noise = noise or (lambda t: t)
     ids = torch.as_tensor(tokens, dtype=torch.long)
     x = rms_norm(w["embed"].to(dt)[ids], w["embed.norm"].to(dt), eps)
     embedded = x
@@ -195,14 +221,14 @@ def forward(cfg, w, tokens, dt=torch.float64, return_layers=False):
         layer, p = cfg["layers"][i], f"l{i}."
         if again:
             x = x + embedded
-        h = rms_norm(x, w[p + "norm1"].to(dt), eps)
+        h = noise(rms_norm(x, w[p + "norm1"].to(dt), eps))
         mix = sink_attention if layer["type"] == "attention" else delta_mixer
-        x = x + rms_norm(mix(h, w, p + "mix.", layer["mixer"], eps, dt), w[p + "norm1b"].to(dt), eps)
+        x = x + rms_norm(noise(mix(h, w, p + "mix.", layer["mixer"], eps, dt)), w[p + "norm1b"].to(dt), eps)
         mlp = layer.get("mlp")
         if mlp is not None:
-            h = rms_norm(x, w[p + "norm2"].to(dt), eps)
-            y = dense_ff(h, w, p + "mlp.", dt) if mlp["kind"] == "dense" else moe_ff(h, w, p + "mlp.", mlp, dt)
-            x = x + rms_norm(y, w[p + "norm2b"].to(dt), eps)
+            h = noise(rms_norm(x, w[p + "norm2"].to(dt), eps))
+            y = dense_ff(h, w, p + "mlp.", dt) if mlp["kind"] == "dense" else moe_ff(h, w, p + "mlp.", mlp, dt, margins)
+            x = x + rms_norm(noise(y), w[p + "norm2b"].to(dt), eps)
         after.append(x)
-    logits = rms_norm(x, w["final.norm"].to(dt), eps) @ w["head"].to(dt).T
+    logits = noise(rms_norm(x, w["final.norm"].to(dt), eps)) @ w["head"].to(dt).T
     return (logits, torch.stack(after)) if return_layers else logits

@@ -25,7 +25,7 @@ attention_decode_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* ou
                         const __nv_bfloat16* kcache, const __nv_bfloat16* vcache,
                         const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
-                        long num_pages, float* part_o, float* part_lse, int* err) {
+                        long num_pages, float* part_o, float* part_lse, int* err, HeadEpilogue ep) {
   extern __shared__ __align__(16) char smem[];
   pdl_launch_dependents();
   const int split = blockIdx.x, num_splits = gridDim.x, kh = blockIdx.y, b = blockIdx.z;
@@ -144,7 +144,8 @@ attention_decode_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* ou
     const float val = L > 0.f ? O / L : 0.f;
     const int head = kh * G + r;
     if (num_splits == 1) {
-      out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(val);
+      const float Ls = L + sink_weight(ep, M);
+      out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(Ls > 0.f ? O / Ls * head_gate(ep, t, head) : 0.f);
     } else {
       const size_t p = ((size_t)b * nh + head) * num_splits + split;
       part_o[p * HD + d] = val;
@@ -177,7 +178,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                             const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                             const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
                             long num_pages, float* part_o, float* part_lse,
-                            int box_keys, int cluster, int* err) {
+                            int box_keys, int cluster, int* err, HeadEpilogue ep) {
   extern __shared__ __align__(1024) char smem_raw[];
   char* smem = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int MERGE_BYTES = (2 * DEC_WARPS * 16 + DEC_WARPS * 16 * HD) * 4;
@@ -366,7 +367,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     const float lse = (L > 0.f && !aborted) ? M + log2f(L) : -INFINITY;
     const int head = kh * G + r;
     if (num_splits == 1) {
-      out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(val);
+      const float Ls = L + sink_weight(ep, M);
+      out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(Ls > 0.f ? O / Ls * head_gate(ep, t, head) : 0.f);
     } else if (cluster) {
       fo[idx] = val;
       if (d == 0) fl[r] = lse;
@@ -412,7 +414,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         W += w;
         O += w * v[sp];
       }
-      out[(size_t)t * nh * HD + (size_t)(kh * G) * HD + idx] = __float2bfloat16_rn(W > 0.f ? O / W : 0.f);
+      W += sink_weight(ep, M);                // the sink counts once, whatever the number of splits
+      out[(size_t)t * nh * HD + (size_t)(kh * G) * HD + idx] =
+          __float2bfloat16_rn(W > 0.f ? O / W * head_gate(ep, t, kh * G + r) : 0.f);
     }
   }
   // nobody may leave while another block still reads its shared memory
@@ -446,7 +450,8 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
                                   const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
                                   const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                                   const int* __restrict__ context_lens, int num_requests, int nh, int kvh, int block_size,
-                                  int window, float scale, long num_pages, int box_keys, unsigned* pairs_taken, int* err) {
+                                  int window, float scale, long num_pages, int box_keys, unsigned* pairs_taken, int* err,
+                                  HeadEpilogue ep) {
   // pairs_taken[0]: pairs given out beyond the first of each block; [1]: blocks that have left
   extern __shared__ __align__(1024) char smem_raw[];
   char* smem = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -663,7 +668,9 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
             L += wl[w * 16 + r] * f;
             O += wo[((size_t)w * G + r) * HD + d] * f;
           }
-          out[(size_t)t * nh * HD + (size_t)(kh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+          L += sink_weight(ep, M);
+          out[(size_t)t * nh * HD + (size_t)(kh * G + r) * HD + d] =
+              __float2bfloat16_rn(L > 0.f ? O / L * head_gate(ep, t, kh * G + r) : 0.f);
         }
       }
       asm volatile("bar.sync 1, %0;\n" ::"n"(DEC_WARPS * 32) : "memory");   // the buffer is free for the next pair
@@ -685,7 +692,7 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
 // Merges the splits of every (decoding request, head): weights 2^(lse - max lse).
 __global__ void attention_decode_combine_kernel(const float* part_o, const float* part_lse,
                                                 __nv_bfloat16* out, const int* __restrict__ cu_q, int nh,
-                                                int num_splits) {
+                                                int num_splits, HeadEpilogue ep) {
   pdl_launch_dependents();
   const int b = blockIdx.y, head = blockIdx.x;
   const int t = cu_q[b];
@@ -703,7 +710,8 @@ __global__ void attention_decode_combine_kernel(const float* part_o, const float
       W += w;
       O += w * part_o[(base + s) * HD + d];
     }
-    out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(W > 0.f ? O / W : 0.f);
+    W += sink_weight(ep, M);
+    out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(W > 0.f ? O / W * head_gate(ep, t, head) : 0.f);
   }
 }
 
@@ -729,7 +737,8 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
                                    const void* kcache, const void* vcache, const int* block_tables, int table_stride,
                                    const int* cu_q, const int* context_lens, int num_requests, int nh, int kvh,
                                    int block_size, int window, float scale, long num_pages, int num_splits, float* scratch,
-                                   unsigned* pairs_counter, int* err, cudaStream_t stream) {
+                                   unsigned* pairs_counter, int* err, cudaStream_t stream,
+                                   HeadEpilogue ep = HeadEpilogue{0, nullptr, 0}) {
   if (num_requests <= 0) return 0;
   if (kvh <= 0 || nh % kvh || nh / kvh > 16 || block_size <= 0 || num_splits < 1 || num_splits > 65535) return VOB_UNSUPPORTED;
   static bool configured = false;
@@ -777,32 +786,32 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
         return launch_kernel(attention_decode_tma_items_kernel, dim3(resident_of[G]), DT_THREADS, items_smem, stream,
                              *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride,
                              (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, num_requests, nh, kvh,
-                             block_size, window, scale, num_pages, box_keys, pairs_counter, err);
+                             block_size, window, scale, num_pages, box_keys, pairs_counter, err, ep);
     }
     // up to 8 splits: the blocks of a (request, kv head) are a cluster and merge through shared memory
     if (num_splits > 1 && num_splits <= 8 && g_decode_cluster_merge)
       return launch_kernel_cluster(attention_decode_tma_kernel, grid, DT_THREADS, tma_smem, stream, (unsigned)num_splits,
                                    *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride,
                                    (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size,
-                                   window, scale, num_pages, part_o, part_lse, box_keys, 1, err);
+                                   window, scale, num_pages, part_o, part_lse, box_keys, 1, err, ep);
     if (num_splits > 1 && !scratch) return VOB_BAD_ARGUMENT;
     rc = launch_kernel(attention_decode_tma_kernel, grid, DT_THREADS, tma_smem, stream, *(const CUtensorMap*)map_k,
                        *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, block_tables,
                        table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, part_o, part_lse,
-                       box_keys, 0, err);
+                       box_keys, 0, err, ep);
     if (rc || num_splits == 1) return rc;
     return launch_kernel(attention_decode_combine_kernel, dim3(nh, num_requests), HD < 128 ? 64 : 128, 0, stream,
-                         (const float*)part_o, (const float*)part_lse, (__nv_bfloat16*)out, cu_q, nh, num_splits);
+                         (const float*)part_o, (const float*)part_lse, (__nv_bfloat16*)out, cu_q, nh, num_splits, ep);
   }
 #endif
   if (num_splits > 1 && !scratch) return VOB_BAD_ARGUMENT;
   rc = launch_kernel(attention_decode_kernel, grid, DEC_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, q_stride,
                          (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,
                          table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, part_o, part_lse,
-                         err);
+                         err, ep);
   if (rc || num_splits == 1) return rc;
   return launch_kernel(attention_decode_combine_kernel, dim3(nh, num_requests), HD < 128 ? 64 : 128, 0, stream,
-                       (const float*)part_o, (const float*)part_lse, (__nv_bfloat16*)out, cu_q, nh, num_splits);
+                       (const float*)part_o, (const float*)part_lse, (__nv_bfloat16*)out, cu_q, nh, num_splits, ep);
 }
 
 // q rows of q_stride elements (head h at h*HD); out [T, nh*HD]; caches [num_pages, kvh, block_size, HD];
@@ -830,6 +839,19 @@ VOB_API int vob_attention_decode_tma(const void* map_k, const void* map_v, const
   return attention_decode_launch(map_k, map_v, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
                                  context_lens, num_requests, nh, kvh, block_size, window, scale, num_pages, num_splits,
                                  scratch, pairs_counter, err, stream);
+}
+
+// Both of the above (null maps: cp.async) with what may follow the softmax: `sink` (a silent extra entry of score 0) and
+// `gate` (bfloat16; head h of token t is multiplied by sigmoid(gate[t * gate_stride + h]); null: none).
+VOB_API int vob_attention_decode_ex(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
+                                    const void* kcache, const void* vcache, const int* block_tables, int table_stride,
+                                    const int* cu_q, const int* context_lens, int num_requests, int nh, int kvh,
+                                    int block_size, int window, float scale, long num_pages, int num_splits,
+                                    float* scratch, unsigned* pairs_counter, int sink, const void* gate, long gate_stride,
+                                    int* err, cudaStream_t stream) {
+  return attention_decode_launch(map_k, map_v, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
+                                 context_lens, num_requests, nh, kvh, block_size, window, scale, num_pages, num_splits,
+                                 scratch, pairs_counter, err, stream, HeadEpilogue{sink, (const __nv_bfloat16*)gate, gate_stride});
 }
 
 VOB_API int vob_attention_decode_has_tma() { return VOB_HD % 64 == 0 ? 1 : 0; }

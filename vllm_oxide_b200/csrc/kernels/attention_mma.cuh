@@ -53,6 +53,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// What may come after the softmax of a head.  `sink`: the softmax has a silent extra entry of score 0 that has no value; it
+// adds 2^(0 - M) to a denominator that is taken relative to M (scores in the base-2 domain).  `gate`: head h of token t is
+// multiplied by sigmoid(gate[t * gate_stride + h]).  {0, nullptr, 0} leaves the softmax as it is.
+struct HeadEpilogue {
+  int sink;
+  const __nv_bfloat16* gate;
+  long gate_stride;
+};
+// The sink's share of a denominator relative to M.  A maximum far below zero gives +inf, and the head's output 0: the limit.
+__device__ __forceinline__ float sink_weight(const HeadEpilogue& ep, float M) { return ep.sink ? exp2f(-M) : 0.f; }
+__device__ __forceinline__ float head_gate(const HeadEpilogue& ep, int t, int head) {
+  if (!ep.gate) return 1.f;
+  const float g = __bfloat162float(ep.gate[(size_t)t * ep.gate_stride + head]);
+  return 1.f / (1.f + __expf(-g));
+}
+
 // The largest of three (one instruction on this architecture).
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;

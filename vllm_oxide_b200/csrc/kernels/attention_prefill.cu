@@ -25,7 +25,7 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
                          const __nv_bfloat16* kcache, const __nv_bfloat16* vcache,
                          const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                          const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
-                         long num_pages, int* err) {
+                         long num_pages, int* err, HeadEpilogue ep) {
   extern __shared__ __align__(16) char smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -137,7 +137,8 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (!rvalid[h]) continue;
-    const float inv = st.l[h] > 0.f ? 1.f / st.l[h] : 0.f;
+    const float lsum = st.l[h] + sink_weight(ep, st.m[h]);
+    const float inv = lsum > 0.f ? head_gate(ep, t0 + rtok[h], rhead[h]) / lsum : 0.f;
     __nv_bfloat16* orow = out + (size_t)(t0 + rtok[h]) * nh * HD + (size_t)rhead[h] * HD + tq * 2;
 #pragma unroll
     for (int j = 0; j < DTILES; ++j)
@@ -168,7 +169,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
                              const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
                              const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                              const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
-                             long num_pages, int box_keys, int* err) {
+                             long num_pages, int box_keys, int* err, HeadEpilogue ep) {
   extern __shared__ __align__(1024) char smem_raw[];
   char* smem = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + PT_STAGES * PT_STAGE_BYTES);
@@ -404,7 +405,8 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (!rvalid[h]) continue;
-    const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+    const float lsum = l[h] + sink_weight(ep, m[h]);
+    const float inv = lsum > 0.f ? head_gate(ep, t0 + rtok[h], rhead[h]) / lsum : 0.f;
     __nv_bfloat16* orow = out + (size_t)(t0 + rtok[h]) * nh * HD + (size_t)rhead[h] * HD + tq * 2;
 #pragma unroll
     for (int j = 0; j < DTILES; ++j)
@@ -420,7 +422,8 @@ using namespace vob;
 static int attention_prefill_launch(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
                                     const void* kcache, const void* vcache, const int* block_tables, int table_stride,
                                     const int* cu_q, const int* context_lens, int num_requests, int max_q, int nh, int kvh,
-                                    int block_size, int window, float scale, long num_pages, int* err, cudaStream_t stream) {
+                                    int block_size, int window, float scale, long num_pages, int* err, cudaStream_t stream,
+                                    HeadEpilogue ep = HeadEpilogue{0, nullptr, 0}) {
   if (num_requests <= 0 || max_q <= 1) return 0;
   if (kvh <= 0 || nh % kvh || block_size <= 0 || kvh > 65535 || num_requests > 65535) return VOB_UNSUPPORTED;
   const long rows = (long)max_q * (nh / kvh);
@@ -437,7 +440,7 @@ static int attention_prefill_launch(const void* map_k, const void* map_v, const 
     return launch_kernel(attention_prefill_tma_kernel, grid, PT_THREADS, tma_smem, stream, *(const CUtensorMap*)map_k,
                          *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, block_tables,
                          table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages,
-                         block_size % PT_TILE == 0 ? PT_TILE : RUN_KEYS, err);
+                         block_size % PT_TILE == 0 ? PT_TILE : RUN_KEYS, err, ep);
   }
 #endif
   static bool configured = false;
@@ -450,7 +453,7 @@ static int attention_prefill_launch(const void* map_k, const void* map_v, const 
   dim3 grid((unsigned)((rows + PF_ROWS - 1) / PF_ROWS), kvh, num_requests);
   return launch_kernel(attention_prefill_kernel, grid, PF_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, q_stride,
                        (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,
-                       table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, err);
+                       table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, err, ep);
 }
 
 // max_q: the most tokens any request brings in this step (sizes the grid).
@@ -471,4 +474,16 @@ VOB_API int vob_attention_prefill_tma(const void* map_k, const void* map_v, cons
                                       cudaStream_t stream) {
   return attention_prefill_launch(map_k, map_v, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
                                   context_lens, num_requests, max_q, nh, kvh, block_size, window, scale, num_pages, err, stream);
+}
+
+// Both of the above (null maps: cp.async) with what may follow the softmax: `sink` (a silent extra entry of score 0) and
+// `gate` (bfloat16; head h of token t is multiplied by sigmoid(gate[t * gate_stride + h]); null: none).
+VOB_API int vob_attention_prefill_ex(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
+                                     const void* kcache, const void* vcache, const int* block_tables, int table_stride,
+                                     const int* cu_q, const int* context_lens, int num_requests, int max_q, int nh,
+                                     int kvh, int block_size, int window, float scale, long num_pages, int sink,
+                                     const void* gate, long gate_stride, int* err, cudaStream_t stream) {
+  return attention_prefill_launch(map_k, map_v, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
+                                  context_lens, num_requests, max_q, nh, kvh, block_size, window, scale, num_pages, err, stream,
+                                  HeadEpilogue{sink, (const __nv_bfloat16*)gate, gate_stride});
 }

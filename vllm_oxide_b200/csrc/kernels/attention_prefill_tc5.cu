@@ -71,7 +71,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
                              const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
                              const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                              const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
-                             long num_pages, int box_keys, int* err) {
+                             long num_pages, int box_keys, int* err, HeadEpilogue ep) {
   using C = F5<NQ>;
   constexpr int ST = C::STAGES;
   extern __shared__ __align__(1024) char smem_raw[];
@@ -442,7 +442,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         t5_fence_after();
-        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const float lsum = l + sink_weight(ep, m_ref);       // the sink relative to the row's reference, like every P
+        const float inv = lsum > 0.f ? head_gate(ep, valid ? t0 + tok : t0, head) / lsum : 0.f;
         __nv_bfloat16* orow = out + (size_t)(t0 + tok) * nh * HD + (size_t)head * HD;
         if (o_by_tma && all_rows) {
           // A whole tile leaves through shared memory and the copy engine: its rows go, in the layout a load would have
@@ -531,12 +532,16 @@ VOB_API int vob_attention_prefill_has_tc5() {
 }
 
 // As vob_attention_prefill_tma (same tensor maps: 64-column slices, boxes of vob_attention_decode_box_keys rows), for
-// head sizes 64 and 128.  `query_tiles` is 1 or 2: how many tiles of 128 query rows a block takes.
+// head sizes 64 and 128.  `query_tiles` is 1 or 2: how many tiles of 128 query rows a block takes.  `sink`: the softmax has a
+// silent extra entry of score 0; `gate` (bfloat16, may be null): head h of token t is multiplied by
+// sigmoid(gate[t * gate_stride + h]).
 VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, const void* map_q, const void* map_o, const void* q, long q_stride, void* out,
                                       const int* block_tables, int table_stride, const int* cu_q, const int* context_lens,
                                       int num_requests, int max_q, int nh, int kvh, int block_size, int window, float scale,
-                                      long num_pages, int query_tiles, int* err, cudaStream_t stream) {
+                                      long num_pages, int query_tiles, int sink, const void* gate, long gate_stride,
+                                      int* err, cudaStream_t stream) {
 #if VOB_HD == 64 || VOB_HD == 128
+  const HeadEpilogue ep{sink, (const __nv_bfloat16*)gate, gate_stride};
   if (num_requests <= 0 || max_q <= 1) return 0;
   if (!map_k || !map_v) return VOB_BAD_ARGUMENT;
   if (((uintptr_t)out & 31) || ((uintptr_t)q & 15)) return VOB_BAD_ARGUMENT;     // 32-byte stores, 16-byte copies
@@ -562,7 +567,7 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
                          *(const CUtensorMap*)(o_by_tma ? map_o : map_k), o_by_tma,
                          (const __nv_bfloat16*)q, q_stride,
                          (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size, window,
-                         scale, num_pages, box_keys, err);
+                         scale, num_pages, box_keys, err, ep);
   }
   if (!configured[1]) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, F5<2>::SMEM_BYTES);
@@ -575,7 +580,7 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
                          *(const CUtensorMap*)(o_by_tma ? map_o : map_k), o_by_tma,
                        (const __nv_bfloat16*)q, q_stride,
                        (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size, window,
-                       scale, num_pages, box_keys, err);
+                       scale, num_pages, box_keys, err, ep);
 #else
   return VOB_UNSUPPORTED;
 #endif

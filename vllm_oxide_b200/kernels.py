@@ -471,30 +471,28 @@ def attention_decode_scratch_floats(head_dim: int, num_requests: int, nh: int, n
 
 
 def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, nh, kvh, hd,
-                     window: int, scale: float, num_splits: int, scratch, err, use_tma: bool = True, pairs=None) -> None:
+                     window: int, scale: float, num_splits: int, scratch, err, use_tma: bool = True, pairs=None,
+                     sink: bool = False, gate=None, gate_stride: int = 0) -> None:
     """Requests that bring exactly one token; the others are skipped.  `pairs`: two int32 zeros on the device that belong
     to this caller (`decode_pairs_counter`); with it, one split and more (request, kv head) pairs than blocks fit the GPU
     run as persistent blocks that draw their pairs from it (the kernel leaves it at zero), without it as one block per
-    pair.  Same bits either way."""
-    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, scratch, pairs)
+    pair.  Same bits either way.  `sink`, `gate`, `gate_stride`: as for paged_attention_generic."""
+    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, scratch, pairs, gate)
     assert pairs is None or (pairs.dtype == torch.int32 and pairs.numel() >= 2)
-    assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and (gate is None or gate.dtype == torch.bfloat16)
     L = attention_lib(hd)
+    map_k = map_v = None
     if use_tma and L.vob_attention_decode_has_tma() and kcache.is_contiguous() and vcache.is_contiguous():
         # head sizes that are a multiple of 64: keys and values come in by TMA (about twice cp.async's rate)
         bs = kcache.shape[2]
         keys, slices = L.vob_attention_decode_box_keys(bs), L.vob_attention_decode_box_slices(bs)
         map_k, map_v = tensor_map(kcache.view(-1, hd), keys, slices), tensor_map(vcache.view(-1, hd), keys, slices)
-        _check(L.vob_attention_decode_tma(
-            map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
-            block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[2], window,
-            ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(pairs), _p(err), _stream()),
-            "attention_decode_tma")
-        return
-    _check(L.vob_attention_decode(
-        _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables), block_tables.shape[-1],
-        _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[2], window, ctypes.c_float(scale),
-        ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(err), _stream()), "attention_decode")
+    _check(L.vob_attention_decode_ex(
+        map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
+        block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[2], window,
+        ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(pairs if map_k is not None else None),
+        int(bool(sink)), _p(gate), ctypes.c_long(gate_stride), _p(err), _stream()),
+        "attention_decode_tma" if map_k is not None else "attention_decode")
 
 
 def decode_pairs_counter(device) -> torch.Tensor:
@@ -505,14 +503,16 @@ def decode_pairs_counter(device) -> torch.Tensor:
 
 def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, max_q, nh, kvh,
                       hd, window: int, scale: float, err, use_tma: bool = True, use_tc5: bool = True,
-                      query_tiles: int = 2, tiles_by_tma: bool = True) -> None:
+                      query_tiles: int = 2, tiles_by_tma: bool = True, sink: bool = False, gate=None, gate_stride: int = 0) -> None:
     """Requests that bring more than one token; the others are skipped.  Head sizes 64 and 128 run on the tcgen05
     tensor cores (`use_tc5`; `tiles_by_tma` False makes that kernel bring its query tiles in by cp.async and store its
     output row by row also where TMA could), other multiples of 64 on mma.sync with TMA copies (`use_tma`), the rest with
-    cp.async."""
-    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens)
-    assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    cp.async.  `sink`, `gate`, `gate_stride`: as for paged_attention_generic."""
+    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, gate)
+    assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and (gate is None or gate.dtype == torch.bfloat16)
     L = attention_lib(hd)
+    extras = (int(bool(sink)), _p(gate), ctypes.c_long(gate_stride))
+    map_k = map_v = None
     if use_tma and L.vob_attention_decode_has_tma() and kcache.is_contiguous() and vcache.is_contiguous():
         bs = kcache.shape[2]
         keys, slices = L.vob_attention_decode_box_keys(bs), L.vob_attention_decode_box_slices(bs)
@@ -526,17 +526,13 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
             _check(L.vob_attention_prefill_tc5(
                 map_k, map_v, map_q, map_o, _p(q), ctypes.c_long(q_stride), _p(out), _p(block_tables), block_tables.shape[-1], _p(cu_q),
                 _p(context_lens), num_requests, max_q, nh, kvh, bs, window, ctypes.c_float(scale),
-                ctypes.c_long(kcache.shape[0]), query_tiles, _p(err), _stream()), "attention_prefill_tc5")
+                ctypes.c_long(kcache.shape[0]), query_tiles, *extras, _p(err), _stream()), "attention_prefill_tc5")
             return
-        _check(L.vob_attention_prefill_tma(
-            map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
-            block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, bs, window,
-            ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), _p(err), _stream()), "attention_prefill_tma")
-        return
-    _check(L.vob_attention_prefill(
-        _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables), block_tables.shape[-1],
-        _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, kcache.shape[2], window, ctypes.c_float(scale),
-        ctypes.c_long(kcache.shape[0]), _p(err), _stream()), "attention_prefill")
+    _check(L.vob_attention_prefill_ex(
+        map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
+        block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, kcache.shape[2], window,
+        ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), *extras, _p(err), _stream()),
+        "attention_prefill_tma" if map_k is not None else "attention_prefill")
 
 
 def gemm_f32(a, w, out, bias=None) -> None:

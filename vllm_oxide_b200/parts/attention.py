@@ -212,7 +212,8 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
     elements of each head of `out`.  `sink`: the softmax has a silent extra entry of score 0.  `gate`: a view whose element
     [t, h] (rows `gate_stride` apart) is head h's gate of token t; its output is multiplied by the sigmoid of it."""
     tables = ctx.block_tables[group]
-    if not kernels.has_fast_attention(q.dtype, hd, nh // kvh) or ((sink or gate is not None) and not FAST_SINK_AND_GATE):
+    fast = kernels.has_fast_attention(q.dtype, hd, nh // kvh) and scale > 0.0      # the tcgen05 kernel takes maxima before it scales
+    if not fast or ((sink or gate is not None) and not FAST_SINK_AND_GATE):
         kernels.paged_attention_generic(q, q_stride, out, keys, values, tables, ctx.token_req, ctx.positions, T,
                                         nh, kvh, hd, window, scale, ctx.err, value_dim=value_dim, sink=sink, gate=gate,
                                         gate_stride=gate_stride)
@@ -224,15 +225,16 @@ def paged_attend(q, q_stride, out, keys, values, group: int, ctx, T: int, nh: in
         n = kernels.attention_decode_scratch_floats(hd, B, nh, splits)
         scratch = ctx.ws.get_flat("attention_decode_scratch", n, torch.float32) if n else None
         kernels.attention_decode(q, q_stride, out, keys, values, tables, ctx.cu_q, ctx.context_lens, B, nh,
-                                 kvh, hd, window, scale, splits, scratch, ctx.err, pairs=pairs)
+                                 kvh, hd, window, scale, splits, scratch, ctx.err, pairs=pairs, sink=sink, gate=gate,
+                                 gate_stride=gate_stride)
     if ctx.max_q > 1:
         kernels.attention_prefill(q, q_stride, out, keys, values, tables, ctx.cu_q, ctx.context_lens, B,
-                                  ctx.max_q, nh, kvh, hd, window, scale, ctx.err)
+                                  ctx.max_q, nh, kvh, hd, window, scale, ctx.err, sink=sink, gate=gate, gate_stride=gate_stride)
     return hd
 
 
 # Whether the tensor-core attention kernels take a softmax with a sink and a gate on the heads (else the plain kernel does).
-FAST_SINK_AND_GATE = False
+FAST_SINK_AND_GATE = True
 
 DECODE_BLOCKS_PER_SM = 2   # blocks of the decode attention kernel that fit an SM (its shared memory decides)
 
