@@ -207,7 +207,8 @@ def test_the_router_alone(E, top, count, keep):
 
 
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("H,I,E,top,count,keep", [(64, 32, 8, 2, 2, 1), (50, 33, 5, 5, 1, 1), (128, 96, 16, 4, 4, 2), (64, 200, 3, 1, 3, 2)])
+@pytest.mark.parametrize("H,I,E,top,count,keep", [(64, 32, 8, 2, 2, 1), (50, 33, 5, 5, 1, 1), (128, 96, 16, 4, 4, 2), (64, 200, 3, 1, 3, 2),
+                                                  (200, 264, 6, 2, 3, 2)])
 def test_routed_experts(H, I, E, top, count, keep, dt):
     from vllm_oxide_b200.parts import PartSpec, build_part
     part = build_part("feed_forward", PartSpec("routed_experts", dict(hidden_size=H, expert_size=I, experts=E, top=top, groups=count,
@@ -219,7 +220,9 @@ def test_routed_experts(H, I, E, top, count, keep, dt):
     load(part, w, dt)
     wh = {k: (v.float().double() if k in ("f.router", "f.correction") else held(v, dt)) for k, v in w.items()}
     mlp = dict(kind="moe", expert=dict(ff=I), router=dict(experts=E, top=top, groups=dict(count=count, keep=keep)))
-    for n in (1, 3, 70, 200):
+    # from 256 (token, choice) pairs on, bfloat16 takes the tensor-core product of the experts: widths that end inside its
+    # tiles of 128 rows and its slices of 64 columns, experts with one row and experts with hundreds
+    for n in (1, 3, 70, 200) + ((700,) if H == 200 else ()):
         x = held(rand((n, H), 3 + n), dt)
         got = part.forward(x.to(dt).to(DEV), ff_context(n, dt))
         assert_close(got, P.moe_ff(x, wh, "f.", mlp, torch.float64), dt, f"{n} tokens")

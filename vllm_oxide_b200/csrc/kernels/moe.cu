@@ -107,9 +107,10 @@ moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __
 
 // ---------------------------------------------------------------- sorting by expert
 // One block.  n = tokens * top pairs; slot_of[n]: the row of a pair; row_token[max_rows]: a row's token (-1: padding);
-// tile_expert[max_rows / MOE_TM]: a row tile's expert (-1: past the end).
+// tile_expert[max_rows / MOE_TM]: the expert of every MOE_TM rows (-1: past the end).  An expert's rows are padded to a
+// multiple of `pad`, itself a multiple of MOE_TM (a product with larger row tiles asks for more).
 __global__ void __launch_bounds__(1024)
-moe_align_kernel(const int* ids, int* slot_of, int* row_token, int* tile_expert, int n, int top, int E, int max_rows) {
+moe_align_kernel(const int* ids, int* slot_of, int* row_token, int* tile_expert, int n, int top, int E, int max_rows, int pad) {
   extern __shared__ int align_smem[];
   int* counts = align_smem;          // [E]
   int* offsets = counts + E;         // [E]
@@ -127,7 +128,7 @@ moe_align_kernel(const int* ids, int* slot_of, int* row_token, int* tile_expert,
     int off = 0;
     for (int e = 0; e < E; ++e) {
       offsets[e] = off;
-      const int padded = (counts[e] + MOE_TM - 1) / MOE_TM * MOE_TM;
+      const int padded = (counts[e] + pad - 1) / pad * pad;
       for (int tile = off / MOE_TM; tile < (off + padded) / MOE_TM; ++tile) tile_expert[tile] = e;
       off += padded;
       counts[e] = 0;      // now the expert's cursor
@@ -266,11 +267,11 @@ VOB_API int vob_moe_route(const void* h, const float* w_router, const float* cor
 }
 
 VOB_API int vob_moe_align(const int* ids, int* slot_of, int* row_token, int* tile_expert, int n, int top, int E, int max_rows,
-                          cudaStream_t stream) {
+                          int pad, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (max_rows % MOE_TM || E <= 0 || E > 4096) return VOB_BAD_ARGUMENT;
+  if (pad <= 0 || pad % MOE_TM || max_rows % pad || E <= 0 || E > 4096) return VOB_BAD_ARGUMENT;
   return launch_kernel(moe_align_kernel, dim3(1), 1024, (size_t)2 * E * sizeof(int), stream, ids, slot_of, row_token, tile_expert,
-                       n, top, E, max_rows);
+                       n, top, E, max_rows, pad);
 }
 
 // A: rows of lda elements (`gather`: indexed by the row's token); W [experts, N, K]; C [max_rows, ldc] of `dtype`, or float

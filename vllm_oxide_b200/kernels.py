@@ -28,7 +28,8 @@ ERR_BITS = {1: "a token id outside the vocabulary", 2: "a position beyond max_po
             4: "a cache slot outside the pool", 8: "a block-table entry that names no page",
             16: "a wanted row outside the batch", 32: "a bounded wait inside a kernel ran out",
             0x100: "(in the weight-streaming product)", 0x200: "(in the tcgen05 product)", 0x400: "(in decode attention)",
-            0x800: "(in the attention for portions, mma.sync)", 0x1000: "(in the attention for portions, tcgen05)"}
+            0x800: "(in the attention for portions, mma.sync)", 0x1000: "(in the attention for portions, tcgen05)",
+            0x2000: "(in the experts' tcgen05 product)"}
 
 
 def lib():
@@ -317,12 +318,43 @@ def moe_route(h, w_router, correction, ids, weights, num_tokens: int, top: int, 
                                _code(h.dtype), _stream()), "moe_route")
 
 
-def moe_align(ids, slot_of, row_token, tile_expert, n: int, top: int, experts: int) -> None:
+def moe_align(ids, slot_of, row_token, tile_expert, n: int, top: int, experts: int, pad: Optional[int] = None) -> None:
     """Sorts n (token, choice) pairs by expert: slot_of[n] a pair's row, row_token[rows] a row's token or -1, tile_expert
-    [rows / moe_row_tile()] a row tile's expert or -1."""
+    [rows / moe_row_tile()] the expert of every moe_row_tile() rows or -1.  An expert's rows are padded to `pad` rows (a
+    multiple of moe_row_tile(), which is the default)."""
     _cuda(ids, slot_of, row_token, tile_expert)
     _check(lib().vob_moe_align(_p(ids), _p(slot_of), _p(row_token), _p(tile_expert), n, top, experts, row_token.numel(),
-                               _stream()), "moe_align")
+                               int(pad or moe_row_tile()), _stream()), "moe_align")
+
+
+def moe_tc5_row_tile() -> int:
+    """Rows of a row tile of the tcgen05 product of the experts."""
+    return int(lib().vob_moe_tc5_row_tile())
+
+
+def moe_gemm_tc5_supported(a, w) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.is_contiguous()
+            and w.is_contiguous() and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def moe_gemm_tc5(a, w, c, row_token, tile_expert, relu_squared: bool, err) -> None:
+    """c[row] = f(a[row] @ w[expert of the row]^T) on the tcgen05 tensor cores: a [rows, K] bfloat16 already sorted by
+    expert in row tiles of moe_tc5_row_tile(), w [experts, N, K]; c bfloat16 with the squared relu, or float."""
+    _cuda(a, w, c, row_token, tile_expert)
+    E, N, K = w.shape
+    assert moe_gemm_tc5_supported(a, w) and a.shape[0] == row_token.numel() and c.stride(1) == 1
+    assert c.dtype == (torch.bfloat16 if relu_squared else torch.float32)
+    map_w, map_x = tensor_map_2d(w.view(E * N, K), 128), tensor_map_2d(a, 128)
+    _check(lib().vob_moe_gemm_tc5(map_w, map_x, _p(c), ctypes.c_long(c.stride(0)), _p(row_token), _p(tile_expert), a.shape[0], N, K,
+                                  0 if relu_squared else 1, _p(err), _stream()), "moe_gemm_tc5")
+
+
+def moe_gather_rows(x, xs, row_token) -> None:
+    """xs[row] = x[row_token[row]] for the rows that name a token (bfloat16, width a multiple of 8)."""
+    _cuda(x, xs, row_token)
+    assert x.dtype == xs.dtype == torch.bfloat16 and x.stride(1) == 1 and xs.is_contiguous() and xs.shape[1] == x.shape[1]
+    _check(lib().vob_moe_gather_rows(_p(x), ctypes.c_long(x.stride(0)), _p(xs), _p(row_token), xs.shape[0], x.shape[1],
+                                     _stream()), "moe_gather_rows")
 
 
 def moe_gemm(a, w, c, row_token, tile_expert, relu_squared: bool, gather: bool) -> None:

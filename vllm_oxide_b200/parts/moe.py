@@ -23,6 +23,11 @@ from .base import FeedForward, register_part
 from .linear import linear
 
 
+# bfloat16 steps with at least this many (token, choice) pairs run the experts' products on the tcgen05 tensor cores (row
+# tiles of 128); smaller ones on the float-accumulating kernel with row tiles of 64, whose padding costs less there.
+TC5_MIN_PAIRS = 256
+
+
 class ReluSquaredMLP(FeedForward):
     graph_safe = True
 
@@ -75,20 +80,29 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x, ctx):
         T, top = x.shape[0], self.top
-        n, tile = T * top, kernels.moe_row_tile()
+        n = T * top
+        # bfloat16 steps of many pairs: the experts' products on the tcgen05 tensor cores, over rows gathered into expert order
+        fast = (n >= TC5_MIN_PAIRS and kernels.moe_gemm_tc5_supported(x, self.wup) and self.I % 8 == 0)
+        tile = kernels.moe_tc5_row_tile() if fast else kernels.moe_row_tile()
         # every expert's rows are padded to a row tile: at most tile - 1 rows for each expert that has any
         max_rows = (n + min(self.E, n) * (tile - 1) + tile - 1) // tile * tile
         ids = ctx.ws.get_flat("moe_ids", n, torch.int32)
         weights = ctx.ws.get_flat("moe_weights", n, torch.float32)
         slot_of = ctx.ws.get_flat("moe_slot_of", n, torch.int32)
         row_token = ctx.ws.get_flat("moe_row_token", max_rows, torch.int32)
-        tile_expert = ctx.ws.get_flat("moe_tile_expert", max_rows // tile, torch.int32)
+        tile_expert = ctx.ws.get_flat("moe_tile_expert", max_rows // kernels.moe_row_tile(), torch.int32)
         kernels.moe_route(x, self.router, self.correction, ids, weights, T, top, self.groups, self.keep)
-        kernels.moe_align(ids, slot_of, row_token, tile_expert, n, top, self.E)
+        kernels.moe_align(ids, slot_of, row_token, tile_expert, n, top, self.E, pad=tile)
         act = ctx.ws.get_flat("moe_act", max_rows * self.I, x.dtype).view(max_rows, self.I)
-        kernels.moe_gemm(x, self.wup, act, row_token, tile_expert, relu_squared=True, gather=True)
         y = ctx.ws.get_flat("moe_y", max_rows * self.H, torch.float32).view(max_rows, self.H)
-        kernels.moe_gemm(act, self.wdown, y, row_token, tile_expert, relu_squared=False, gather=False)
+        if fast:
+            rows = ctx.ws.get_flat("moe_rows", max_rows * self.H, x.dtype).view(max_rows, self.H)
+            kernels.moe_gather_rows(x, rows, row_token)
+            kernels.moe_gemm_tc5(rows, self.wup, act, row_token, tile_expert, True, ctx.err)
+            kernels.moe_gemm_tc5(act, self.wdown, y, row_token, tile_expert, False, ctx.err)
+        else:
+            kernels.moe_gemm(x, self.wup, act, row_token, tile_expert, relu_squared=True, gather=True)
+            kernels.moe_gemm(act, self.wdown, y, row_token, tile_expert, relu_squared=False, gather=False)
         out = ctx.ws.get("mlp_out", T, self.H, x.dtype)
         kernels.moe_combine(y, slot_of, weights, out, T, top)
         return out
