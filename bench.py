@@ -18,10 +18,11 @@ of 8 requests whose context starts at 2,048 tokens, and prints ONE JSON line:
 The cache that the decode steps read was written by a real prefill of random prompts.  Every timed step reads 15 GB of weights, far more than the 126 MB L2, so nothing stays cached
 between iterations.  Peaks come from MEASURED_PEAKS.json beside this file when present.
 
-    python bench.py --workload tofilorn [--sizes 2048,4096]
+    python bench.py --workload tofilorn | kesozen [--sizes 2048,4096]
 
-measures the Tofilorn design (residual streams, minGRU, HGRN2, latent attention) at layer sizes of 1B- and 8B-class
-models beside Qwen3 at the same width, depth and feed-forward size: one 2,048-token prompt in one step, decode at batch 8
+measures the Tofilorn design (residual streams, minGRU, HGRN2, latent attention) or the Kesozen design (sandwich norms over
+a float stream, attention whose keys are its values, gated delta rule, routed experts) at layer sizes of 1B- and 8B-class
+models beside Qwen3 at the same width, depth and feed-forward size (Kesozen also beside Tofilorn): one 2,048-token prompt in one step, decode at batch 8
 and 64 from a 2,048-token context (CUDA graphs), and, from an eager engine with the per-kernel timers on, the time of each
 of this package's kernels in those steps with the bytes it must move against the copy bandwidth.
 
@@ -375,6 +376,47 @@ def tofilorn_kernel_bytes(cfg: dict, T: int) -> dict:
     return b
 
 
+def kesozen_config(width: int, layers: int) -> dict:
+    """Layer sizes of a real model of this width: a block of four layers (three gated delta rules, then attention whose keys
+    are its values); feed-forwards of 16 experts of which a token uses 4 (the four together three times the width), but
+    for the second layer of each block, whose feed-forward is dense and three times the width; heads of 128."""
+    heads = width // 128
+    att = dict(heads=heads, kv_heads=8, dim=128, vdim=128, scale=128 ** -0.5, rot={"dims": 64, "base": 10000.0})
+    delta = dict(heads=heads, kv_heads=max(1, heads // 2), dim=128, vdim=128, conv=4)
+    moe = {"kind": "moe", "expert": {"ff": 3 * width // 4}, "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    dense = {"kind": "dense", "ff": 3 * width}
+    out = []
+    for _ in range(0, layers, 4):
+        out += [{"type": "delta", "mixer": delta, "mlp": moe}, {"type": "delta", "mixer": delta, "mlp": dense},
+                {"type": "delta", "mixer": delta, "mlp": moe}, {"type": "attention", "mixer": att, "mlp": moe}]
+    return {"architecture": "Kesozen", "vocab": 32768, "width": width, "norm": {"eps": 1e-6}, "layers": out[:layers]}
+
+
+def kesozen_kernel_bytes(cfg: dict, T: int) -> dict:
+    """Bytes that each of the design's own row-wise kernels must move in a step of T tokens, summed over the layers (weights
+    aside): what its time is held against.  The scan and the experts' products are held against arithmetic instead."""
+    D = cfg["width"]
+    b = {"residual_norm_step": T * (D * 2 + D * 4 + D * 2) + T * D * 4}          # the embedding's norm; the last norm reads the stream
+    for l in cfg["layers"]:
+        m, mlp = l["mixer"], l["mlp"]
+        subs = 2 if mlp else 1
+        b["residual_norm_step"] += subs * T * (2 * D * 4 + 2 * D * 2)             # stream read and written, y in, normed out
+        if l["type"] == "attention":
+            nh, kvh, hd = m["heads"], m["kv_heads"], m["dim"]
+            b["rope_shared_kv_write"] = b.get("rope_shared_kv_write", 0) + T * ((nh + kvh) + nh + 2 * kvh) * hd * 2
+        else:
+            C, V = 2 * m["kv_heads"] * m["dim"] + m["heads"] * m["vdim"], m["heads"] * m["vdim"]
+            b["short_conv_silu"] = b.get("short_conv_silu", 0) + T * C * (2 + 4)
+            b["delta_out_norm"] = b.get("delta_out_norm", 0) + T * V * (4 + 2 + 2)
+        if mlp and mlp["kind"] == "dense":
+            b["relu_squared"] = b.get("relu_squared", 0) + T * mlp["ff"] * 2 * 2
+        elif mlp:
+            top = mlp["router"]["top"]
+            b["moe_gather_rows"] = b.get("moe_gather_rows", 0) + T * top * D * 2 * 2
+            b["moe_combine"] = b.get("moe_combine", 0) + T * (top * D * 4 + D * 2)
+    return b
+
+
 def qwen3_kernel_bytes(cfg: dict, T: int) -> dict:
     """The same for the row-wise kernels of a Qwen3 step: add+norm reads the stream and writes the normed rows (the sum was made
     by the product before), the q/k kernel reads q|k|v, writes q and k back and k, v to the cache, SiLU*up reads 2I and writes I."""
@@ -384,16 +426,35 @@ def qwen3_kernel_bytes(cfg: dict, T: int) -> dict:
             "qk_norm_rope_kv_write": L * T * ((nh + 2 * kvh) + (nh + kvh) + 2 * kvh) * hd * 2}
 
 
-def tofilorn_run(widths, pk=None, layers: int = 16) -> dict:
+DESIGNS = {"tofilorn": (tofilorn_config, tofilorn_kernel_bytes), "kesozen": (kesozen_config, kesozen_kernel_bytes)}
+
+
+def float_issue_rate():
+    """Float instructions a second the device can issue: SMs x 128 lanes x the largest SM clock (0 if the clock cannot be read)."""
+    import torch
+    try:
+        mhz = float(subprocess.run(["nvidia-smi", "--query-gpu=clocks.max.sm", "--format=csv,noheader,nounits", "-i", "0"],
+                                   capture_output=True, text=True, timeout=20).stdout.split()[0])
+    except (OSError, ValueError, IndexError, subprocess.SubprocessError):
+        mhz = 0.0
+    return torch.cuda.get_device_properties(0).multi_processor_count * 128 * mhz * 1e6
+
+
+def design_run(design: str, widths, pk=None, layers: int = 16) -> dict:
+    """One of the listed-layer designs beside Qwen3 (and, for the scan kernels, beside each other) at equal layer sizes."""
     import torch
     from vllm_oxide_b200 import LLM, EngineOptions, kernels
     pk = pk or peaks()
-    out = {"metric": "tokens/s, Tofilorn beside Qwen3 at equal layer sizes", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+    label = design.capitalize()
+    out = {"metric": f"tokens/s, {label} beside Qwen3 at equal layer sizes", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
            "data": "synthetic token ids, seeded random weights", "peaks": pk, "sizes": {}}
+    bytes_of = {"qwen3": qwen3_kernel_bytes, **{k: v[1] for k, v in DESIGNS.items()}}
     for width in widths:
-        models = {"tofilorn": tofilorn_config(width, layers),
+        models = {design: DESIGNS[design][0](width, layers),
                   "qwen3": dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=width // 128,
                                 num_key_value_heads=8, intermediate_size=3 * width, vocab_size=32768, max_position_embeddings=8192)}
+        if design == "kesozen":
+            models["tofilorn"] = tofilorn_config(width, layers)       # its matrix-state scan is the delta rule's like kernel
         rec = {}
         for name, cfg in models.items():
             r = {}
@@ -421,31 +482,43 @@ def tofilorn_run(widths, pk=None, layers: int = 16) -> dict:
                 torch.cuda.empty_cache()
             if True:
                 for key, T in (("prefill_2048", PROMPT_LEN), ("decode_batch8", 8)):
-                    ms, by = r[key]["own_kernels_ms"], (tofilorn_kernel_bytes if name == "tofilorn" else qwen3_kernel_bytes)(cfg, T)
+                    ms, by = r[key]["own_kernels_ms"], bytes_of[name](cfg, T)
                     r[key]["own_kernels_frac_of_copy"] = {k: round(by[k] / (ms[k] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
                                                           for k in by if ms.get(k)}
                 if name == "tofilorn" and r["prefill_2048"]["own_kernels_ms"].get("hgrn2_scan"):
                     # the matrix-state scan is arithmetic, not traffic: float instructions a lane must issue (two walks of a
                     # cut portion: multiply + multiply-add, then multiply + two multiply-adds, per state element and token)
                     # against the device's float issue rate (SMs x 128 lanes x clock)
-                    prop = torch.cuda.get_device_properties(0)
-                    try:
-                        mhz = float(subprocess.run(["nvidia-smi", "--query-gpu=clocks.max.sm", "--format=csv,noheader,nounits", "-i", "0"],
-                                                   capture_output=True, text=True, timeout=20).stdout.split()[0])
-                    except (OSError, ValueError, IndexError, subprocess.SubprocessError):
-                        mhz = 0.0
-                    rate = prop.multi_processor_count * 128 * mhz * 1e6
+                    rate = float_issue_rate()
                     work = sum(PROMPT_LEN * l["mixer"]["heads"] * l["mixer"]["dim"] * l["mixer"]["vdim"] * 5
                                for l in cfg["layers"] if l["type"] == "hgrn2")
                     if rate:
                         r["prefill_2048"]["hgrn2_scan_frac_of_float_issue_rate"] = round(
                             work / (r["prefill_2048"]["own_kernels_ms"]["hgrn2_scan"] * 1e-3) / rate, 4)
+                if name == "kesozen":
+                    own = r["prefill_2048"]["own_kernels_ms"]
+                    if own.get("delta_scan"):
+                        # the delta rule is arithmetic too: a multiply and three multiply-adds per state element and token
+                        rate = float_issue_rate()
+                        work = sum(PROMPT_LEN * l["mixer"]["heads"] * l["mixer"]["dim"] * l["mixer"]["vdim"] * 4
+                                   for l in cfg["layers"] if l["type"] == "delta")
+                        if rate:
+                            r["prefill_2048"]["delta_scan_frac_of_float_issue_rate"] = round(work / (own["delta_scan"] * 1e-3) / rate, 4)
+                    if own.get("moe_gemm_tc5"):
+                        # the experts' products against the measured bfloat16 product of the library
+                        flops = sum(4 * PROMPT_LEN * l["mlp"]["router"]["top"] * cfg["width"] * l["mlp"]["expert"]["ff"]
+                                    for l in cfg["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe")
+                        r["prefill_2048"]["moe_gemm_tc5_frac_of_bf16_peak"] = round(flops / (own["moe_gemm_tc5"] * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
             rec[name] = r
         out["sizes"][str(width)] = rec
-    out["value"] = out["sizes"][str(widths[0])]["tofilorn"]["decode_batch8"]["tokens_per_s"]
+    out["value"] = out["sizes"][str(widths[0])][design]["decode_batch8"]["tokens_per_s"]
     out["config"] = {"layers": layers, "widths": list(widths), "prompt": PROMPT_LEN, "block_size": BLOCK,
                      "l2": "weights of a step exceed L2 at every size"}
     return out
+
+
+def tofilorn_run(widths, pk=None, layers: int = 16) -> dict:
+    return design_run("tofilorn", widths, pk, layers)
 
 
 def attention_kernels_run(pk) -> dict:
@@ -540,9 +613,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (reported)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["tofilorn"], default=None,
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(DESIGNS), default=None,
                     help="another workload instead of the default run")
-    ap.add_argument("--sizes", default="2048,4096", help="--workload tofilorn: the widths to measure")
+    ap.add_argument("--sizes", default="2048,4096", help="--workload tofilorn | kesozen: the widths to measure")
     ap.add_argument("--only", choices=["decode", "prefill", "attention"], default=None,
                     help="run one phase and print its time only (for short profiler captures)")
     args = ap.parse_args()
@@ -553,8 +626,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (use --gpus 1)")
         return 2
-    if args.workload == "tofilorn":
-        print(json.dumps(tofilorn_run([int(w) for w in args.sizes.split(",")])))
+    if args.workload in DESIGNS:
+        print(json.dumps(design_run(args.workload, [int(w) for w in args.sizes.split(",")])))
         return 0
     if args.workload:
         print(json.dumps(workload_run(args.workload)))

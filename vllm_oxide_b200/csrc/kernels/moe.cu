@@ -33,11 +33,13 @@ __device__ __forceinline__ Best warp_best(Best x) {
   return x;
 }
 
+constexpr int ROUTE_NT = 256;
+
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(ROUTE_NT)
 moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __restrict__ correction, int* ids, float* weights,
                  int W, int E, int top, int count, int keep) {
-  extern __shared__ float route_smem[];
+  extern __shared__ __align__(16) float route_smem[];
   float* hrow = route_smem;          // [W]
   float* score = hrow + W;           // [E] softmax
   float* choice = score + E;         // [E] score + correction, -inf once taken or shut out
@@ -45,12 +47,26 @@ moe_route_kernel(const T* h, const float* __restrict__ w_router, const float* __
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int d = threadIdx.x; d < W; d += 128) hrow[d] = to_f<T>(h[(size_t)t * W + d]);
+  for (int d = threadIdx.x; d < W; d += ROUTE_NT) hrow[d] = to_f<T>(h[(size_t)t * W + d]);
   __syncthreads();
-  for (int e = warp; e < E; e += 4) {
+  // a warp takes experts warp, warp + 8, ...; a lane sums four elements at a time into four chains (one chain where the
+  // width is no multiple of 4): the order of a logit's additions depends on the width alone
+  const bool vec = W % 4 == 0 && ((uintptr_t)w_router % 16) == 0;
+  for (int e = warp; e < E; e += ROUTE_NT / 32) {
     const float* wr = w_router + (size_t)e * W;
     float z = 0.f;
-    for (int d = lane; d < W; d += 32) z = fmaf(hrow[d], wr[d], z);
+    if (vec) {
+      float z4[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int d = lane * 4; d < W; d += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(wr + d);
+        const float4 hv = *reinterpret_cast<const float4*>(hrow + d);
+        z4[0] = fmaf(hv.x, wv.x, z4[0]); z4[1] = fmaf(hv.y, wv.y, z4[1]);
+        z4[2] = fmaf(hv.z, wv.z, z4[2]); z4[3] = fmaf(hv.w, wv.w, z4[3]);
+      }
+      z = (z4[0] + z4[1]) + (z4[2] + z4[3]);
+    } else {
+      for (int d = lane; d < W; d += 32) z = fmaf(hrow[d], wr[d], z);
+    }
     z = warp_sum(z);
     if (lane == 0) score[e] = z;
   }
@@ -223,10 +239,105 @@ moe_combine_kernel(const float* y, const int* slot_of, const float* weights, T* 
   for (int d = threadIdx.x; d < D; d += 256) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j) {
-      const int row = slot_of[(size_t)t * top + j];
+      const int row = slot_of ? slot_of[(size_t)t * top + j] : t * top + j;
       if (row >= 0) acc = fmaf(weights[(size_t)t * top + j], y[(size_t)row * D + d], acc);
     }
     out[(size_t)t * D + d] = from_f<T>(acc);
+  }
+}
+
+// ---------------------------------------------------------------- steps of few tokens (bfloat16)
+// While decoding, a step has fewer (token, choice) pairs than a row tile has rows, and the products are bound by the
+// experts' weights, not by arithmetic.  moe_order lists the pairs by expert, without padding; moe_gemv gives a pair a
+// block per 64 output features: the pair's input row lies in shared memory, a warp streams four rows of W_e at a time
+// with 16-byte loads and sums in float.  Pairs of one expert run side by side, so its rows come from DRAM once.
+__global__ void __launch_bounds__(256)
+moe_order_kernel(const int* ids, int* order, int n, int E) {
+  extern __shared__ int order_smem[];
+  int* counts = order_smem;          // [E], then the experts' cursors
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = counts[e];
+      counts[e] = off;
+      off += c;
+    }
+    for (int j = off; j < n; ++j) order[j] = -1;      // pairs that name no expert
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) order[atomicAdd(&counts[e], 1)] = i;
+  }
+}
+
+constexpr int MV_ROWS = 64;       // output features a block
+
+// EPI 0: float as it is; 1: squared relu into bfloat16.  BY_TOKEN: a pair's input row is its token's (pair / top), else its own.
+template <int EPI, bool BY_TOKEN>
+__global__ void __launch_bounds__(256)
+moe_gemv_kernel(const __nv_bfloat16* A, long lda, const __nv_bfloat16* __restrict__ W, void* C, long ldc, const int* ids,
+                const int* order, int top, int N, int K) {
+  extern __shared__ uint4 gemv_smem[];     // the input row: K bfloat16
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pair = order[blockIdx.y];
+  if (pair < 0) return;
+  const int e = ids[pair];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunks = K / 8;
+  const uint4* arow = reinterpret_cast<const uint4*>(A + (size_t)(BY_TOKEN ? pair / top : pair) * lda);
+  for (int c = threadIdx.x; c < chunks; c += 256) gemv_smem[c] = arow[c];
+  __syncthreads();
+  const int n0 = blockIdx.x * MV_ROWS + warp * 8;
+#pragma unroll
+  for (int rg = 0; rg < 2; ++rg) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint4* wrow[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int n = min(n0 + rg * 4 + r, N - 1);
+      wrow[r] = reinterpret_cast<const uint4*>(W + ((size_t)e * N + n) * K);
+    }
+    for (int c = lane; c < chunks; c += 32) {
+      uint4 wv[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) wv[r] = wrow[r][c];
+      const uint4 xv = gemv_smem[c];
+      const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv[r]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 wf = __bfloat1622float2(w2[j]), xf = __bfloat1622float2(x2[j]);
+          acc[r] = fmaf(wf.x, xf.x, acc[r]);
+          acc[r] = fmaf(wf.y, xf.y, acc[r]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const float v = warp_sum(acc[r]);
+      const int n = n0 + rg * 4 + r;
+      if (lane == 0 && n < N) {
+        if (EPI == 1) {
+          const float p = fmaxf(v, 0.f);
+          reinterpret_cast<__nv_bfloat16*>(C)[(size_t)pair * ldc + n] = __float2bfloat16_rn(p * p);
+        } else {
+          reinterpret_cast<float*>(C)[(size_t)pair * ldc + n] = v;
+        }
+      }
+    }
   }
 }
 
@@ -257,7 +368,7 @@ VOB_API int vob_moe_route(const void* h, const float* w_router, const float* cor
   do {                                                                                                                   \
     if (smem > 48 * 1024)                                                                                                \
       cudaFuncSetAttribute(moe_route_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
-    return launch_kernel(moe_route_kernel<TYPE>, dim3(T), 128, smem, stream, (const TYPE*)h, w_router, correction, ids,   \
+    return launch_kernel(moe_route_kernel<TYPE>, dim3(T), ROUTE_NT, smem, stream, (const TYPE*)h, w_router, correction, ids, \
                          weights, W, E, top, count, keep);                                                               \
   } while (0)
   if (dtype == VOB_F32) VOB_ROUTE(float);
@@ -294,6 +405,33 @@ VOB_API int vob_moe_gemm(const void* A, long lda, const void* W, void* C, long l
 #undef VOB_MG_TYPE
 #undef VOB_MG
   return VOB_BAD_ARGUMENT;
+}
+
+VOB_API int vob_moe_order(const int* ids, int* order, int n, int E, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (E <= 0 || E > 4096) return VOB_BAD_ARGUMENT;
+  return launch_kernel(moe_order_kernel, dim3(1), 256, (size_t)E * sizeof(int), stream, ids, order, n, E);
+}
+
+// A: bfloat16 rows of lda elements, a token's (`by_token`) or a pair's; W bfloat16 [experts, N, K], K a multiple of 8;
+// C [pairs, ldc]: bfloat16 with the squared relu (`relu2`) or float.  order: the pairs by expert (vob_moe_order).
+VOB_API int vob_moe_gemv(const void* A, long lda, const void* W, void* C, long ldc, const int* ids, const int* order, int n,
+                         int top, int N, int K, int relu2, int by_token, cudaStream_t stream) {
+  if (n <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || (lda * 2) % 16 || ((uintptr_t)A | (uintptr_t)W) % 16 || n > 65535) return VOB_UNSUPPORTED;
+  const size_t smem = (size_t)K * 2;
+  if (smem > 96 * 1024) return VOB_UNSUPPORTED;
+  dim3 grid((N + MV_ROWS - 1) / MV_ROWS, n);
+#define VOB_MV(EPI, BT)                                                                                                     \
+  do {                                                                                                                      \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_gemv_kernel<EPI, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    return launch_kernel(moe_gemv_kernel<EPI, BT>, grid, 256, smem, stream, (const __nv_bfloat16*)A, lda,                   \
+                         (const __nv_bfloat16*)W, C, ldc, ids, order, top, N, K);                                          \
+  } while (0)
+  if (relu2 && by_token) VOB_MV(1, true);
+  if (!relu2 && !by_token) VOB_MV(0, false);
+#undef VOB_MV
+  return VOB_UNSUPPORTED;
 }
 
 VOB_API int vob_moe_combine(const float* y, const int* slot_of, const float* weights, void* out, int T, int D, int top, int dtype,

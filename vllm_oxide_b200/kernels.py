@@ -282,7 +282,7 @@ def short_conv_state(x, channels: int, taps: int, state, conv_off: int, cu_q, st
 def delta_scan(qkv, ab, b_off: int, a_off: int, A_log, dt_bias, state, cu_q, state_slots, raw, num_requests: int, heads: int,
                kvh: int, dim: int, vdim: int, err) -> None:
     """The gated delta rule over every request's tokens of this step, from and to its slot (state [slots, n] float, the
-    heads' matrices [heads, dim, vdim] first).  qkv float [tokens, 2 kvh dim + heads vdim]; ab: rows whose elements
+    heads' matrices first, each stored column by column, [heads, vdim, dim]).  qkv float [tokens, 2 kvh dim + heads vdim]; ab: rows whose elements
     b_off + h and a_off + h are head h's pre-activations of beta and of the decay; raw float [tokens, heads * vdim]."""
     _cuda(qkv, ab, A_log, dt_bias, state, cu_q, state_slots, raw)
     assert qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[1] == 2 * kvh * dim + heads * vdim
@@ -368,8 +368,30 @@ def moe_gemm(a, w, c, row_token, tile_expert, relu_squared: bool, gather: bool) 
                               _code(a.dtype), _stream()), "moe_gemm")
 
 
+def moe_order(ids, order, n: int, experts: int) -> None:
+    """order[n]: the step's (token, choice) pairs listed by expert, without padding (-1 behind the last)."""
+    _cuda(ids, order)
+    _check(lib().vob_moe_order(_p(ids), _p(order), n, experts, _stream()), "moe_order")
+
+
+def moe_gemv_supported(a, w, n: int) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.shape[1] <= 48 * 1024
+            and a.stride(1) == 1 and (a.stride(0) * 2) % 16 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and w.is_contiguous() and n <= 65535)
+
+
+def moe_gemv(a, w, c, ids, order, n: int, top: int, relu_squared: bool) -> None:
+    """c[pair] = f(a[pair or its token] @ w[expert of the pair]^T) for the step's pairs, few of them (decoding): bfloat16,
+    bound by the experts' rows, which a warp streams with 16-byte loads.  relu_squared: the first product (a by token, c
+    bfloat16); else the second (a by pair, c float)."""
+    _cuda(a, w, c, ids, order)
+    assert moe_gemv_supported(a, w, n) and c.stride(1) == 1 and c.dtype == (torch.bfloat16 if relu_squared else torch.float32)
+    _check(lib().vob_moe_gemv(_p(a), ctypes.c_long(a.stride(0)), _p(w), _p(c), ctypes.c_long(c.stride(0)), _p(ids), _p(order), n,
+                              top, w.shape[1], w.shape[2], int(relu_squared), int(relu_squared), _stream()), "moe_gemv")
+
+
 def moe_combine(y, slot_of, weights, out, num_tokens: int, top: int) -> None:
-    """out[t] = sum_j weights[t, j] * y[slot_of[t, j]] (float, j in order)."""
+    """out[t] = sum_j weights[t, j] * y[slot_of[t, j]] (float, j in order); slot_of None: pair (t, j) is row t * top + j."""
     _cuda(y, slot_of, weights, out)
     assert y.dtype == torch.float32 and y.is_contiguous() and out.is_contiguous()
     _check(lib().vob_moe_combine(_p(y), _p(slot_of), _p(weights), _p(out), num_tokens, out.shape[1], top, _code(out.dtype),

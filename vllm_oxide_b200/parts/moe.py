@@ -24,7 +24,8 @@ from .linear import linear
 
 
 # bfloat16 steps with at least this many (token, choice) pairs run the experts' products on the tcgen05 tensor cores (row
-# tiles of 128); smaller ones on the float-accumulating kernel with row tiles of 64, whose padding costs less there.
+# tiles of 128); smaller ones stream the experts' rows pair by pair (moe_gemv).  The 32-bit path, and widths those two
+# refuse, take the float-accumulating kernel with row tiles of 64.
 TC5_MIN_PAIRS = 256
 
 
@@ -83,11 +84,24 @@ class RoutedExperts(FeedForward):
         n = T * top
         # bfloat16 steps of many pairs: the experts' products on the tcgen05 tensor cores, over rows gathered into expert order
         fast = (n >= TC5_MIN_PAIRS and kernels.moe_gemm_tc5_supported(x, self.wup) and self.I % 8 == 0)
+        ids = ctx.ws.get_flat("moe_ids", n, torch.int32)
+        weights = ctx.ws.get_flat("moe_weights", n, torch.float32)
+        if (not fast and x.dtype == torch.bfloat16 and self.I % 8 == 0 and kernels.moe_gemv_supported(x, self.wup, n)):
+            # bfloat16 steps of few pairs (decoding): nothing is sorted into tiles; the pairs are listed by expert and each
+            # streams its expert's rows
+            order = ctx.ws.get_flat("moe_order", n, torch.int32)
+            kernels.moe_route(x, self.router, self.correction, ids, weights, T, top, self.groups, self.keep)
+            kernels.moe_order(ids, order, n, self.E)
+            act = ctx.ws.get_flat("moe_act", n * self.I, x.dtype).view(n, self.I)
+            kernels.moe_gemv(x, self.wup, act, ids, order, n, top, True)
+            y = ctx.ws.get_flat("moe_y", n * self.H, torch.float32).view(n, self.H)
+            kernels.moe_gemv(act, self.wdown, y, ids, order, n, top, False)
+            out = ctx.ws.get("mlp_out", T, self.H, x.dtype)
+            kernels.moe_combine(y, None, weights, out, T, top)
+            return out
         tile = kernels.moe_tc5_row_tile() if fast else kernels.moe_row_tile()
         # every expert's rows are padded to a row tile: at most tile - 1 rows for each expert that has any
         max_rows = (n + min(self.E, n) * (tile - 1) + tile - 1) // tile * tile
-        ids = ctx.ws.get_flat("moe_ids", n, torch.int32)
-        weights = ctx.ws.get_flat("moe_weights", n, torch.float32)
         slot_of = ctx.ws.get_flat("moe_slot_of", n, torch.int32)
         row_token = ctx.ws.get_flat("moe_row_token", max_rows, torch.int32)
         tile_expert = ctx.ws.get_flat("moe_tile_expert", max_rows // kernels.moe_row_tile(), torch.int32)
