@@ -351,6 +351,23 @@ __global__ void relu_squared_kernel(const T* x, T* out, size_t total) {
   }
 }
 
+// The same with 16-byte accesses (bfloat16, a multiple of 8 elements, aligned).
+__global__ void relu_squared_vec_kernel(const uint4* x, uint4* out, size_t chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += (size_t)gridDim.x * blockDim.x) {
+    uint4 v = x[i];
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(h[j]);
+      f.x = fmaxf(f.x, 0.f); f.y = fmaxf(f.y, 0.f);
+      h[j] = __floats2bfloat162_rn(f.x * f.x, f.y * f.y);
+    }
+    out[i] = v;
+  }
+}
+
 }  // namespace vob
 
 using namespace vob;
@@ -449,6 +466,11 @@ VOB_API int vob_relu_squared(const void* x, void* out, long total, int dtype, cu
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (dtype == VOB_F32)
     return launch_kernel(relu_squared_kernel<float>, dim3(blocks), 256, 0, stream, (const float*)x, (float*)out, (size_t)total);
+  if (dtype == VOB_BF16 && total % 8 == 0 && ((uintptr_t)x | (uintptr_t)out) % 16 == 0) {
+    const long chunks = total / 8;
+    const int vblocks = (int)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
+    return launch_kernel(relu_squared_vec_kernel, dim3(vblocks), 256, 0, stream, (const uint4*)x, (uint4*)out, (size_t)chunks);
+  }
   if (dtype == VOB_BF16)
     return launch_kernel(relu_squared_kernel<__nv_bfloat16>, dim3(blocks), 256, 0, stream, (const __nv_bfloat16*)x,
                          (__nv_bfloat16*)out, (size_t)total);
