@@ -385,7 +385,8 @@ def test_the_command_line(folders):
 
 def random_config(rng, kinds=None):
     """Sizes drawn at random, odd ones among them: no size of the design may rest on another, or on being a power of two.
-    Attention heads are held to three widths so that bfloat16 needs no further attention libraries."""
+    Attention heads are held to three widths of the tensor-core kernels, so that bfloat16 needs no further attention
+    libraries, and two that only the plain kernel takes."""
     width = rng.choice([34, 50, 72, 96, 110, 136])
     if kinds is None:
         kinds = ["attention", "delta"] + [rng.choice(["attention", "delta"]) for _ in range(rng.randint(0, 3))]
@@ -395,7 +396,7 @@ def random_config(rng, kinds=None):
         kv = rng.randint(1, 3)
         heads = kv * rng.randint(1, 3)
         if kind == "attention":
-            dim = rng.choice([32, 64, 128])
+            dim = rng.choice([32, 64, 128, 24, 36])      # the last two: no tensor-core attention, the plain kernel in both precisions
             layer = _attention(heads, kv, dim, rng.choice([0.05, 0.2, 0.5]), 2 * rng.randint(0, dim // 2), rng.choice([100.0, 10000.0, 777.0]))
         else:
             layer = _delta(heads, kv, rng.randint(3, 70), rng.randint(3, 140), rng.randint(1, 6))

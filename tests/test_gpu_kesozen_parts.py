@@ -66,7 +66,7 @@ def attention_part(dt, H, nh, kvh, hd, scale, rot):
 
 @pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("case", ["part of the head rotated", "one key head", "whole head rotated, 128 wide", "nothing rotated",
-                                  "as many key heads as heads", "scores far below the sink"])
+                                  "as many key heads as heads", "scores far below the sink", "a head of 20", "a head of 40"])
 def test_shared_kv_attention_alone_with_loud_keys(case, dt):
     bs = 16
     if case == "part of the head rotated":
@@ -79,6 +79,10 @@ def test_shared_kv_attention_alone_with_loud_keys(case, dt):
         H, spec = 48, (3, 3, 16, 0.3, None)
     elif case == "as many key heads as heads":
         H, spec = 32, (5, 5, 32, 0.25, dict(dims=2, base=100.0))
+    elif case == "a head of 20":               # no 16-byte loads, the plain kernel in both precisions
+        H, spec = 40, (3, 1, 20, 0.3, dict(dims=6, base=50.0))
+    elif case == "a head of 40":
+        H, spec = 48, (4, 2, 40, 0.2, dict(dims=40, base=1000.0))
     else:
         H, spec = 40, (4, 2, 32, -3.0, dict(dims=8, base=300.0))    # a negative scale: the loud keys' own scores are far below 0
     part, w, m = attention_part(dt, H, *spec)

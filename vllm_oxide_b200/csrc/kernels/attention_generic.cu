@@ -4,7 +4,8 @@
 //
 // One block per (token, query head).  The keys a query may read are lo..pos, with
 // pos the query's position and lo = max(0, pos - window + 1) (0 without a window).  They are
-// walked in tiles of 32 ALIGNED TO ABSOLUTE POSITIONS; tile j belongs to warp j % 4.  Each
+// walked in tiles of 32 ALIGNED TO ABSOLUTE POSITIONS; tile j belongs to warp j % 4.  Any head size up to 512 (16-byte
+// loads where a head's rows allow them).  Each
 // warp keeps a running maximum, sum and weighted value sum in float (an online softmax), and
 // the four warps are merged in a fixed order.  So the sequence of float operations for a
 // query depends only on (lo, pos) and on the cache's contents at those positions: not on how
@@ -25,6 +26,10 @@ __device__ __forceinline__ float dot_row(const float* q, const T* k, int hd);
 template <>
 __device__ __forceinline__ float dot_row<float>(const float* q, const float* k, int hd) {
   float s = 0.f;
+  if (hd % 4) {                        // rows that do not start on 16-byte boundaries: element by element
+    for (int i = 0; i < hd; ++i) s += q[i] * k[i];
+    return s;
+  }
   const float4* k4 = reinterpret_cast<const float4*>(k);
   for (int i = 0; i < hd / 4; ++i) {
     const float4 v = k4[i];
@@ -37,6 +42,10 @@ template <>
 __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* q, const __nv_bfloat16* k,
                                                          int hd) {
   float s = 0.f;
+  if (hd % 8) {                        // rows that do not start on 16-byte boundaries: element by element
+    for (int i = 0; i < hd; ++i) s += q[i] * __bfloat162float(k[i]);
+    return s;
+  }
   const uint4* k8 = reinterpret_cast<const uint4*>(k);
   for (int i = 0; i < hd / 8; ++i) {
     const uint4 raw = k8[i];
@@ -159,7 +168,7 @@ VOB_API int vob_paged_attention_generic(const void* q, long q_stride, void* out,
                                         int window, float scale, long num_pages, int sink, const void* gate,
                                         long gate_stride, int dtype, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hd <= 0 || hd % 16 || hd > 512 || kvh <= 0 || nh % kvh || block_size <= 0 || vd <= 0 || vd > hd) return VOB_UNSUPPORTED;
+  if (hd <= 0 || hd > 512 || kvh <= 0 || nh % kvh || block_size <= 0 || vd <= 0 || vd > hd) return VOB_UNSUPPORTED;
   dim3 grid(T, nh);
   const size_t smem = (size_t)(1 + ATT_WARPS) * hd * sizeof(float);
   if (dtype == VOB_F32)

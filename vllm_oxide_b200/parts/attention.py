@@ -153,8 +153,9 @@ class SharedKVAttention(Mixer):
                  names=("q", "k", "g", "o"), **_):
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
-        if head_dim % 16 or head_dim > 512:
-            raise ValueError(f"head_dim {head_dim} is not supported by the attention kernels (a multiple of 16 up to 512)")
+        if not 0 < head_dim <= 512:
+            raise ValueError(f"head_dim {head_dim} is not supported by the attention kernels (up to 512; the tensor-core "
+                             f"kernels take multiples of 16 up to 256, the plain kernel the rest)")
         self.H, self.nh, self.kvh, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
         self.scale, self.sink, self.gate, self.window = float(scale), bool(sink), bool(gate), int(window or 0)
         if position is not None and position not in positions:
