@@ -18,7 +18,7 @@ DTYPES = [torch.float32, torch.bfloat16]
 
 # ---------------------------------------------------------------- the stream and its norms
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("D", [64, 50, 33, 320, 4096, 8200])
+@pytest.mark.parametrize("D", [64, 50, 33, 344, 4096, 8200])
 def test_residual_norm_step(D, dt):
     from vllm_oxide_b200 import kernels
     n, eps = 7, 1e-5
@@ -179,7 +179,7 @@ def ff_context(n, dt):
 
 
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("H,I", [(64, 128), (50, 33), (320, 1000)])
+@pytest.mark.parametrize("H,I", [(64, 128), (50, 33), (344, 1000)])
 def test_relu_squared_mlp(H, I, dt):
     from vllm_oxide_b200.parts import PartSpec, build_part
     part = build_part("feed_forward", PartSpec("relu2_mlp", dict(hidden_size=H, intermediate_size=I, prefix="f.")), positions={}, dtype=dt, device=DEV)
