@@ -7,7 +7,7 @@
 // channel, `taps` taps, the last one the current token's) followed by SiLU; the last taps - 1 inputs of every channel are
 // part of the request's state, behind S in the same slot.  Query/key head h / (heads / kv_heads) serves value head h.
 //
-// Four kernels:
+// Four kernels (short_conv_step is the first two in one, for steps of short portions):
 //   short_conv_silu    out[t, c] = SiLU(sum_j w[c, j] x[t - (taps-1) + j, c]), inputs before the portion's start from the slot
 //   short_conv_state   the slot's taps - 1 inputs after this portion (run after the first: it overwrites what that one reads)
 //   delta_scan         the recurrence.  A column of S lives in the registers of LANES threads (ROWS rows each, rows
@@ -105,6 +105,53 @@ short_conv_state_kernel(const T* x, long x_stride, float* state, long state_stri
 #pragma unroll
   for (int s = 0; s < DELTA_MAX_TAPS - 1; ++s)
     if (s < taps - 1) st[(size_t)s * C + c] = nv[s];
+}
+
+// Both of the above in one launch for steps whose portions are short (decoding): a thread owns one channel of one request,
+// takes its window from the slot, walks the request's few tokens and leaves the window in the slot.  The same sums in the
+// same order as the two kernels.
+template <typename T>
+__global__ void __launch_bounds__(128)
+short_conv_step_kernel(const T* x, long x_stride, const float* __restrict__ w, float* state, long state_stride, long conv_off,
+                       const int* __restrict__ cu_q, const int* __restrict__ state_slots, float* out, int C, int taps,
+                       long num_slots, int* err) {
+  pdl_launch_dependents();
+  const int b = blockIdx.y;
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  const int t0 = cu_q[b], n = cu_q[b + 1] - t0;
+  const int slot = state_slots[b];
+  float wt[DELTA_MAX_TAPS];
+#pragma unroll
+  for (int s = 0; s < DELTA_MAX_TAPS; ++s) wt[s] = (c < C && s < taps) ? w[(size_t)c * taps + s] : 0.f;
+  const float w_now = c < C ? w[(size_t)c * taps + taps - 1] : 0.f;
+  pdl_wait();
+  if (n <= 0) return;
+  if (slot < 0 || slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(err, VOB_ERR_SLOT);
+    return;
+  }
+  if (c >= C) return;
+  float* st = state + (size_t)slot * state_stride + conv_off;
+  float win[DELTA_MAX_TAPS - 1];
+#pragma unroll
+  for (int s = 0; s < DELTA_MAX_TAPS - 1; ++s) win[s] = s < taps - 1 ? st[(size_t)s * C + c] : 0.f;
+  for (int i = 0; i < n; ++i) {
+    const float cur = to_f<T>(x[(size_t)(t0 + i) * x_stride + c]);
+    float acc = 0.f;
+#pragma unroll
+    for (int s = 0; s < DELTA_MAX_TAPS - 1; ++s)
+      if (s < taps - 1) acc = fmaf(wt[s], win[s], acc);
+    acc = fmaf(w_now, cur, acc);
+    out[(size_t)(t0 + i) * C + c] = silu_f(acc);
+#pragma unroll
+    for (int s = 0; s < DELTA_MAX_TAPS - 1; ++s) {
+      if (s < taps - 2) win[s] = win[s + 1 < DELTA_MAX_TAPS - 1 ? s + 1 : s];
+      else if (s == taps - 2) win[s] = cur;
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < DELTA_MAX_TAPS - 1; ++s)
+    if (s < taps - 1) st[(size_t)s * C + c] = win[s];
 }
 
 // ---------------------------------------------------------------- the recurrence
@@ -337,6 +384,21 @@ VOB_API int vob_short_conv_state(const void* x, long x_stride, float* state, lon
   if (dtype == VOB_BF16)
     return launch_kernel(short_conv_state_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)x, x_stride,
                          state, state_stride, conv_off, cu_q, state_slots, C, taps, num_slots);
+  return VOB_BAD_ARGUMENT;
+}
+
+VOB_API int vob_short_conv_step(const void* x, long x_stride, const float* w, float* state, long state_stride, long conv_off,
+                                const int* cu_q, const int* state_slots, float* out, int B, int C, int taps, long num_slots,
+                                int dtype, int* err, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (C <= 0 || taps < 1 || taps > DELTA_MAX_TAPS || B > 65535) return VOB_UNSUPPORTED;
+  dim3 grid((C + 127) / 128, B);
+  if (dtype == VOB_F32)
+    return launch_kernel(short_conv_step_kernel<float>, grid, 128, 0, stream, (const float*)x, x_stride, w, state, state_stride,
+                         conv_off, cu_q, state_slots, out, C, taps, num_slots, err);
+  if (dtype == VOB_BF16)
+    return launch_kernel(short_conv_step_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)x, x_stride, w,
+                         state, state_stride, conv_off, cu_q, state_slots, out, C, taps, num_slots, err);
   return VOB_BAD_ARGUMENT;
 }
 

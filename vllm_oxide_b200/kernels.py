@@ -279,6 +279,18 @@ def short_conv_state(x, channels: int, taps: int, state, conv_off: int, cu_q, st
                                       ctypes.c_long(state.shape[0]), _code(x.dtype), _stream()), "short_conv_state")
 
 
+def short_conv_step(x, channels: int, taps_w, state, conv_off: int, cu_q, state_slots, out, num_requests: int, err) -> None:
+    """short_conv_silu and short_conv_state in one launch, a thread a (request, channel): for steps whose portions are
+    short (decoding).  Same numbers."""
+    _cuda(x, taps_w, state, cu_q, state_slots, out)
+    assert x.stride(1) == 1 and taps_w.dtype == torch.float32 and taps_w.is_contiguous() and taps_w.shape[0] == channels
+    assert state.dtype == torch.float32 and state.is_contiguous() and out.dtype == torch.float32 and out.is_contiguous()
+    _check(lib().vob_short_conv_step(_p(x), ctypes.c_long(x.stride(0)), _p(taps_w), _p(state), ctypes.c_long(state.stride(0)),
+                                     ctypes.c_long(conv_off), _p(cu_q), _p(state_slots), _p(out), num_requests, channels,
+                                     taps_w.shape[1], ctypes.c_long(state.shape[0]), _code(x.dtype), _p(err), _stream()),
+           "short_conv_step")
+
+
 def delta_scan(qkv, ab, b_off: int, a_off: int, A_log, dt_bias, state, cu_q, state_slots, raw, num_requests: int, heads: int,
                kvh: int, dim: int, vdim: int, err) -> None:
     """The gated delta rule over every request's tokens of this step, from and to its slot (state [slots, n] float, the

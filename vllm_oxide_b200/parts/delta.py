@@ -27,6 +27,9 @@ from .base import Mixer, StateSpec, register_part
 from .linear import linear
 
 
+SHORT_PORTIONS = 8      # up to this many tokens a request, the convolution and its state are one kernel
+
+
 class GatedDelta(Mixer):
     graph_safe = True
 
@@ -73,9 +76,14 @@ class GatedDelta(Mixer):
         T, B = x.shape[0], ctx.launch_requests
         proj = linear(x, self.w_in, ctx.ws.get("delta_in", T, self.width, x.dtype), ctx)
         qkv = ctx.ws.get("delta_qkv", T, self.channels, torch.float32)
-        kernels.short_conv_silu(proj, self.channels, self.conv_w, state, self.matrix_floats, ctx.token_req, ctx.cu_q,
-                                ctx.state_slots, qkv, T, ctx.err)
-        kernels.short_conv_state(proj, self.channels, self.taps, state, self.matrix_floats, ctx.cu_q, ctx.state_slots, B)
+        if ctx.max_q <= SHORT_PORTIONS:
+            # short portions (decoding): a thread a (request, channel) does the filter and leaves the slot's inputs, one launch
+            kernels.short_conv_step(proj, self.channels, self.conv_w, state, self.matrix_floats, ctx.cu_q, ctx.state_slots,
+                                    qkv, B, ctx.err)
+        else:
+            kernels.short_conv_silu(proj, self.channels, self.conv_w, state, self.matrix_floats, ctx.token_req, ctx.cu_q,
+                                    ctx.state_slots, qkv, T, ctx.err)
+            kernels.short_conv_state(proj, self.channels, self.taps, state, self.matrix_floats, ctx.cu_q, ctx.state_slots, B)
         raw = ctx.ws.get("delta_raw", T, self.nh * self.dv, torch.float32)
         kernels.delta_scan(qkv, proj, self.b_off, self.a_off, self.A_log, self.dt_bias, state, ctx.cu_q, ctx.state_slots, raw,
                            B, self.nh, self.kvh, self.dk, self.dv, ctx.err)
